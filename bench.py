@@ -1,0 +1,333 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N=1): INT8 attention forward at B=4 H=32 S=4096 D=128, bf16 inputs ~N(0,1) with 1 % of
+the channels scaled x20, seeded, non-causal.  One step = quantize Q, K, V per token (3 launches of
+the quantizer; V also written dequantized) + one int8 attention forward.  `value` = attention ops
+4*B*H*D*S^2 per step / step time, in TOPS, inputs resident in HBM.  With N > 1 every rank runs
+the same per-GPU workload on its own heads (global batch 4*N, no collective on the data path):
+weak scaling.  Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+B, H, S, D = 4, 32, 4096, 128
+WORKLOAD = "int8_attn_fwd B4 H32 S4096 D128 non-causal bf16 outlier-channels (quantize q,k,v + forward)"
+
+
+def fwd_ops(b, h, sq, skv, d, causal=False):
+    pairs = sq * skv if not causal else sq * (sq + 1) // 2
+    return 4 * b * h * d * pairs
+
+
+def make_inputs(b, h, s, d, device, seed_base, head0=0, dtype=torch.bfloat16):
+    """Per-(batch, head) seeded generation so that any partition of the heads sees the same data."""
+    out = []
+    for t in range(3):
+        x = torch.empty(b * h, s, d, dtype=dtype, device=device)
+        for i in range(b * h):
+            g = torch.Generator(device=device).manual_seed(seed_base + 1000 * t + head0 + i)
+            x[i] = torch.randn(s, d, generator=g, device=device, dtype=torch.float32).to(dtype)
+        g = torch.Generator().manual_seed(seed_base + 7 + t)
+        idx = torch.randperm(d, generator=g)[: max(1, math.ceil(0.01 * d))]
+        x[..., idx.to(device)] *= 20.0
+        out.append(x.view(b, h, s, d))
+    return out
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.lines, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# --------------------------------------------------------------------------------------------- CPU arm
+
+def cpu_reference_sample(heads: int, s: int, d: int, repeats: int, causal=False):
+    """Times the CPU restatement of the reference math (per-token quantize -> dequantized softmax
+    attention) on `heads` heads of the workload; returns (ops per second, seconds, threads)."""
+    import oracle
+    torch.manual_seed(0)
+    q, k, v = (torch.randn(1, heads, s, d).bfloat16() for _ in range(3))
+    sm = 1.0 / math.sqrt(d)
+    oracle.int8_mode_forward(q[:, :1, :256], k[:, :1, :256], v[:, :1, :256], causal, sm)   # warm-up
+    t0 = time.perf_counter()
+    for _ in range(repeats):
+        oracle.int8_mode_forward(q, k, v, causal, sm)
+    dt = time.perf_counter() - t0
+    return fwd_ops(1, heads, s, s, d, causal) * repeats / dt, dt, torch.get_num_threads()
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    heads = 2
+    # warm-up steps and timed steps each run the bounded sample once
+    for _ in range(min(args.warmup, 1)):
+        cpu_reference_sample(1, 1024, D, 1)
+    t0 = time.perf_counter()
+    ops = 0.0
+    for _ in range(args.steps):
+        rate, dt, threads = cpu_reference_sample(heads, S, D, 1)
+        ops += rate * dt
+    el = time.perf_counter() - t0
+    value = ops / el / 1e12
+    sample = f"{heads} of {B * H} heads of the workload per step (S={S}, D={D}), oracle port in PyTorch CPU fp32"
+    line = {
+        "impl": "reference", "metric": "int8_attention_forward_throughput", "value": value, "unit": "TOPS",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": el / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8*int8->int32 + bf16",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "TOPS", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------------- GPU arm
+
+def run_ours(args):
+    import torch.distributed as dist
+    import quant_flash_attn_b200 as qfa
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sm = 1.0 / math.sqrt(D)
+    # every rank owns B*H heads of a global batch of B*world
+    q, k, v = make_inputs(B, H, S, D, dev, seed_base=1234, head0=rank * B * H)
+    ops_step = fwd_ops(B, H, S, S, D, False)
+    stream = torch.cuda.current_stream()
+
+    o = torch.empty_like(q)
+    lse = torch.empty(B, H, S, dtype=torch.float32, device=dev)
+
+    def step(record=None):
+        qq, kq, vq = qfa.quantize_qkv(q, k, v)
+        if record is not None:
+            record[0].record(stream)
+        qfa.int8_attention_forward(qq, kq, vq, False, sm, torch.bfloat16, o=o, lse=lse)
+        if record is not None:
+            record[1].record(stream)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = qfa.launch_count()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t_begin.record(stream)
+    for i in range(args.steps):
+        step(ev[i])
+    t_end.record(stream)
+    barrier()
+    launches = qfa.launch_count() - launches0
+    ms_total = t_begin.elapsed_time(t_end)
+    attn_ms = sum(a.elapsed_time(b) for a, b in ev) / args.steps
+    if world > 1:
+        t = torch.tensor([ms_total, attn_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total, attn_ms = t.tolist()
+    clocks = sampler.stop() if rank == 0 else None
+    ms_step = ms_total / args.steps
+    value = ops_step * world / (ms_step * 1e-3) / 1e12
+
+    # ---- secondary figures (rank-local, untimed region): quantizer GB/s, causal forward, fwd+bwd
+    def time_ms(fn, reps=10, warm=3):
+        for _ in range(warm):
+            fn()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record(stream)
+        for _ in range(reps):
+            fn()
+        b.record(stream)
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+
+    extra = {}
+    if rank == 0:
+        n_tok = B * H * S
+        big = torch.randn(8, 32, 4096, D, device=dev, dtype=torch.bfloat16)   # 268 MB in: larger than L2
+        q_ms = time_ms(lambda: qfa.asymmetric_quant_per_token_ex(big))
+        q_bytes = big.numel() // D * (2 * D + D + 2 + 1 + 4)
+        extra["quantizer"] = {"tokens": big.numel() // D, "D": D, "ms": q_ms, "GBps": q_bytes / q_ms / 1e6,
+                              "bytes_per_token": 2 * D + D + 7}
+        del big
+        qq, kq, vq = qfa.quantize_qkv(q, k, v)
+        c_ms = time_ms(lambda: qfa.int8_attention_forward(qq, kq, vq, True, sm, torch.bfloat16, o=o, lse=lse))
+        extra["fwd_causal"] = {"ms": c_ms, "TOPS": fwd_ops(B, H, S, S, D, True) / c_ms / 1e9}
+        n_ms = time_ms(lambda: qfa.int8_attention_forward(qq, kq, vq, False, sm, torch.bfloat16, o=o, lse=lse))
+        extra["fwd_noncausal_kernel"] = {"ms": n_ms, "TOPS": ops_step / n_ms / 1e9}
+        # training shape: B8 H16 S2048 D64 causal, forward + backward (ops = 3.5 x forward)
+        tb, th, ts, td = 8, 16, 2048, 64
+        tq, tk, tv = make_inputs(tb, th, ts, td, dev, seed_base=99)
+        tdo = torch.randn_like(tq)
+        tsm = 1.0 / math.sqrt(td)
+
+        def train_step():
+            a, b_, c = (t.detach().requires_grad_() for t in (tq, tk, tv))
+            out = qfa.quant_attention(a, b_, c, True, tsm)
+            out.backward(tdo)
+        t_ms = time_ms(train_step, reps=5)
+        extra["fwd_bwd_B8H16S2048D64_causal"] = {"ms": t_ms, "TOPS": 3.5 * fwd_ops(tb, th, ts, ts, td, True) / t_ms / 1e9}
+        del tq, tk, tv, tdo
+
+    # ---- end to end through the public operator with host buffers (pinned), every step H2D + D2H
+    hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
+    ho = torch.empty(q.shape, dtype=q.dtype).pin_memory()
+    dq_, dk_, dv_ = (torch.empty_like(t) for t in (q, k, v))
+
+    def e2e_step():
+        dq_.copy_(hq, non_blocking=True)
+        dk_.copy_(hk, non_blocking=True)
+        dv_.copy_(hv, non_blocking=True)
+        out = qfa.quant_attention(dq_, dk_, dv_, False, sm)
+        ho.copy_(out, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    b_.record(stream)
+    barrier()
+    e2e_ms = a.elapsed_time(b_) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = t.item()
+    e2e = {"value": ops_step * world / (e2e_ms * 1e-3) / 1e12, "unit": "TOPS",
+           "h2d_bytes_per_step": 3 * q.numel() * q.element_size(), "d2h_bytes_per_step": q.numel() * q.element_size(),
+           "ms_per_step": e2e_ms, "steps": e2e_steps}
+
+    if rank == 0:
+        peaks = load_peaks()
+        long_run = ms_total > 2000.0
+        peak = peaks["bf16_tflops_sustained"] if long_run else peaks["bf16_tflops"]
+        achieved = ops_step / (attn_ms * 1e-3) / 1e12
+        roofline = {
+            "bound": "tensor", "kernel": "int8 attention forward", "achieved": achieved, "peak": peak,
+            "unit": "TFLOP/s", "frac": achieved / peak,
+            "peak_kind": ("sustained" if long_run else "burst") + " bf16 dense, of " + peaks["source"],
+            "frac_of_mixed_int8_bf16": achieved / (1.0 / (0.5 / (2 * peak) + 0.5 / peak)),
+            "frac_of_int8_nominal_4500": achieved / 4500.0,
+            "traffic": None, "ms_per_launch": attn_ms,
+        }
+        if "quantizer" in extra:
+            extra["quantizer"]["frac_of_hbm_" + peaks["source"]] = extra["quantizer"]["GBps"] / peaks["hbm_gbs"]
+        cpu_rate, cpu_dt, threads = cpu_reference_sample(2, S, D, 2)
+        cpu_baseline = {"value": cpu_rate / 1e12, "unit": "TOPS", "cores": threads, "kind": "port",
+                        "sample": f"2 of {B * H} heads (S={S}, D={D}) x2 repeats, {cpu_dt:.1f} s, PyTorch CPU fp32 oracle"}
+        line = {
+            "metric": "int8_attention_forward_throughput", "value": value, "unit": "TOPS", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "int8*int8->int32 + bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "global_batch": B * world, "heads": H, "seq_len": S, "head_dim": D,
+                       "partition": f"heads x{world}", "l2": "inputs (3 x 134 MB) larger than the 126 MB L2"},
+            "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches,
+            "clocks": clocks, "extra": extra,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

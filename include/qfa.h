@@ -1,0 +1,172 @@
+/*
+ * qfa.h -- C ABI of libqfa_sm100a.so: per-token asymmetric INT8 quantizer and
+ * INT8 flash attention (forward, backward) for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes raw DEVICE pointers, sizes and element strides; the
+ * library allocates no user-visible memory, launches on the stream it is given
+ * and returns without synchronising.  Return value: 0 = launched; negative =
+ * argument rejected before any launch (see qfa_strerror).  Kernels that wait on
+ * hardware barriers use bounded waits; when a wait runs out they store a positive
+ * code into the caller's `status` word (device memory, may be NULL) and return.
+ *
+ * "Reference" in the comments is the Triton project this library is a drop-in
+ * for on this path; citations are file:line in that project.
+ */
+#ifndef QFA_H_
+#define QFA_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* qfa_stream_t;
+
+#if defined(__GNUC__)
+#define QFA_API __attribute__((visibility("default")))
+#else
+#define QFA_API
+#endif
+
+/* dtype codes for 16-bit floating tensors */
+#define QFA_F16 0
+#define QFA_BF16 1
+
+/* numeric mode of the attention kernels */
+#define QFA_MODE_REF 0  /* Q stays 16-bit, logits from a 16-bit MMA on dequantized K (the reference's math) */
+#define QFA_MODE_INT8 1 /* Q and K int8, logits from an int8 x int8 -> int32 MMA plus zero-point corrections */
+
+/* error codes (negative: rejected on the host; positive: reported by a kernel) */
+#define QFA_OK 0
+#define QFA_ERR_NULL -1        /* a required pointer is NULL */
+#define QFA_ERR_DTYPE -2       /* dtype code is not QFA_F16 / QFA_BF16 */
+#define QFA_ERR_SHAPE -3       /* a size is <= 0 or too large for the kernel */
+#define QFA_ERR_HEAD_DIM -4    /* head dimension not supported by this entry point */
+#define QFA_ERR_STRIDE -5      /* innermost stride must be 1 / row stride not supported */
+#define QFA_ERR_ALIGN -6       /* pointer or stride not aligned for vector / TMA access */
+#define QFA_ERR_MODE -7        /* unknown mode, or operands missing for the mode */
+#define QFA_ERR_CUDA -8        /* a CUDA runtime / driver call failed (see qfa_last_cuda_error) */
+#define QFA_ERR_TOO_LARGE -9   /* size exceeds the fixed capacity of a no-allocation entry point */
+#define QFA_STATUS_WAIT_TIMEOUT 1 /* a bounded mbarrier wait inside a kernel ran out */
+
+/* ---------------------------------------------------------------------------------------------
+ * Quantizer.  Replaces the launch in asymmetric_quant_per_token (asymmetric_quant.py:109-149) and
+ * the kernel _asymmetric_quant_kernel (asymmetric_quant.py:32-106).
+ *
+ *   x        (Z,H,M,D) fp16/bf16, element strides sx_z, sx_h, sx_m, sx_k (any values)
+ *   codes    int8, written with the SAME strides as x (asymmetric_quant.py:64,127)
+ *   scale    fp16 bits, contiguous (Z*H*M)          (asymmetric_quant.py:93)
+ *   zp       int8, contiguous (Z*H*M)               (asymmetric_quant.py:94)
+ *   rowsum   int32 sum of each row's codes, contiguous (Z*H*M); may be NULL.  Not in the
+ *            reference; the int8 attention path needs it.
+ * Results are bit-identical to the reference kernel's.
+ */
+QFA_API int qfa_quant_per_token(const void* x, int8_t* codes, uint16_t* scale_f16, int8_t* zp,
+                        int32_t* rowsum_or_null,
+                        int64_t Z, int64_t H, int64_t M, int64_t D,
+                        int64_t sx_z, int64_t sx_h, int64_t sx_m, int64_t sx_k,
+                        int dtype, qfa_stream_t stream);
+
+/* Same quantizer; additionally writes the dequantized row (code - zp) * fp16(scale), rounded to
+ * `dtype`, i.e. the operand the reference builds in registers at quant_flash_attn.py:65-66.
+ * `dequant` is contiguous (Z,H,M,D) and may be NULL. */
+QFA_API int qfa_quant_dequant_per_token(const void* x, int8_t* codes, uint16_t* scale_f16, int8_t* zp,
+                                int32_t* rowsum_or_null, void* dequant_or_null,
+                                int64_t Z, int64_t H, int64_t M, int64_t D,
+                                int64_t sx_z, int64_t sx_h, int64_t sx_m, int64_t sx_k,
+                                int dtype, qfa_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * One quantized operand of the attention kernels: codes (B,H,S,D) with element strides (inner
+ * stride 1), and per-token scale / zero-point / code-sum arrays contiguous over (B*H*S).
+ */
+typedef struct {
+  const int8_t* codes;
+  int64_t stride[3];     /* batch, head, token strides of codes, in elements */
+  const uint16_t* scale; /* fp16 bits */
+  const int8_t* zp;
+  const int32_t* rowsum; /* needed for Q and K in QFA_MODE_INT8, else may be NULL */
+} QfaQuantTensor;
+
+/* Forward.  Replaces QuantFlashAttention.forward's launch (quant_flash_attn.py:179-204) and the
+ * kernel _attn_fwd_kernel_quantized (quant_flash_attn.py:27-83); `causal` follows
+ * flash_attn_triton.py:441,50 (row >= column, top-left aligned).
+ *
+ * QFA_MODE_REF : q (16-bit) is read, `qq` is ignored.  k and v may be the same tensor.
+ * QFA_MODE_INT8: qq, k (codes + scale + zp + rowsum) feed the int8 MMA; q is ignored.
+ * v_hat (optional, 16-bit, contiguous (B,H,Skv,D)): dequantized V as written by
+ * qfa_quant_dequant_per_token; when NULL the kernel dequantizes v's codes itself.
+ * o: 16-bit (B,H,Sq,D) with strides; lse: fp32, row b*H+h starts at lse + (b*H+h)*lse_stride.
+ */
+typedef struct {
+  int32_t mode, dtype, causal;
+  float sm_scale;
+  int64_t B, H, Sq, Skv, D;
+  const void* q;
+  int64_t q_stride[3];
+  QfaQuantTensor qq, k, v;
+  const void* v_hat;
+  void* o;
+  int64_t o_stride[3];
+  float* lse;
+  int64_t lse_stride;
+  int32_t* status; /* device int32 or NULL */
+} QfaFwdArgs;
+
+QFA_API int qfa_attn_fwd(const QfaFwdArgs* args, qfa_stream_t stream);
+
+/* Backward pre-pass, delta[row] = sum_d O*dO.  Replaces _bwd_preprocess_kernel
+ * (quant_flash_attn.py:88-101).  o and d_o are 16-bit (B,H,Sq,D) with their own strides. */
+QFA_API int qfa_attn_bwd_delta(const void* o, const int64_t o_stride[3], const void* d_o,
+                       const int64_t do_stride[3], float* delta, int64_t delta_stride,
+                       int64_t B, int64_t H, int64_t Sq, int64_t D, int dtype, qfa_stream_t stream);
+
+/* Backward.  Replaces QuantFlashAttention.backward's main launch (quant_flash_attn.py:225-235) and
+ * _bwd_kernel_quantized (quant_flash_attn.py:109-166).
+ *
+ * Forward operands as in QfaFwdArgs, plus lse and delta (same row stride), d_o, and outputs:
+ *   dq            16-bit (B,H,Sq,D)
+ *   dk, dv        16-bit (B,H,Skv,D).  If `dkv_fused` is non-zero only `dk` is written and holds
+ *                 dV + sm_scale*dK as the reference does (quant_flash_attn.py:161); requires k == v.
+ * dq_accum: fp32 scratch, contiguous (B,H,Sq,D), owned by the caller; the kernel zero-fills it,
+ * accumulates dQ into it with atomics and converts it into dq.
+ * Gradients: dq = sm_scale * dS.K^, dk = sm_scale * dS^T.Q, dv = P^T.dO.
+ */
+typedef struct {
+  int32_t mode, dtype, causal, dkv_fused;
+  float sm_scale;
+  int64_t B, H, Sq, Skv, D;
+  const void* q;
+  int64_t q_stride[3];
+  QfaQuantTensor qq, k, v;
+  const void* d_o;
+  int64_t do_stride[3];
+  const float* lse;
+  const float* delta;
+  int64_t lse_stride;
+  void* dq;
+  int64_t dq_stride[3];
+  void* dk;
+  int64_t dk_stride[3];
+  void* dv;
+  int64_t dv_stride[3];
+  float* dq_accum;
+  int32_t* status;
+} QfaBwdArgs;
+
+QFA_API int qfa_attn_bwd(const QfaBwdArgs* args, qfa_stream_t stream);
+
+/* Text for a return / status code. */
+QFA_API const char* qfa_strerror(int code);
+/* Last CUDA error string seen by this library on the calling thread ("" if none). */
+QFA_API const char* qfa_last_cuda_error(void);
+/* ABI version of this header. */
+QFA_API int qfa_version(void);
+/* Number of kernel launches issued by this library since load (all threads). */
+QFA_API int64_t qfa_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QFA_H_ */

@@ -1,0 +1,98 @@
+"""ctypes binding of libqfa_sm100a.so (the C ABI declared in include/qfa.h).
+
+There is no fallback: if the shared library is missing or cannot be loaded, every
+operator of this package raises.  Build it with `python -m quant_flash_attn_b200.build`.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import threading
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libqfa_sm100a.so")
+
+QFA_F16, QFA_BF16 = 0, 1
+QFA_MODE_REF, QFA_MODE_INT8 = 0, 1
+
+c_i64x3 = C.c_int64 * 3
+
+
+class QfaQuantTensor(C.Structure):
+    _fields_ = [("codes", C.c_void_p), ("stride", c_i64x3), ("scale", C.c_void_p),
+                ("zp", C.c_void_p), ("rowsum", C.c_void_p)]
+
+
+class QfaFwdArgs(C.Structure):
+    _fields_ = [("mode", C.c_int32), ("dtype", C.c_int32), ("causal", C.c_int32), ("sm_scale", C.c_float),
+                ("B", C.c_int64), ("H", C.c_int64), ("Sq", C.c_int64), ("Skv", C.c_int64), ("D", C.c_int64),
+                ("q", C.c_void_p), ("q_stride", c_i64x3),
+                ("qq", QfaQuantTensor), ("k", QfaQuantTensor), ("v", QfaQuantTensor),
+                ("v_hat", C.c_void_p), ("o", C.c_void_p), ("o_stride", c_i64x3),
+                ("lse", C.c_void_p), ("lse_stride", C.c_int64), ("status", C.c_void_p)]
+
+
+class QfaBwdArgs(C.Structure):
+    _fields_ = [("mode", C.c_int32), ("dtype", C.c_int32), ("causal", C.c_int32), ("dkv_fused", C.c_int32),
+                ("sm_scale", C.c_float),
+                ("B", C.c_int64), ("H", C.c_int64), ("Sq", C.c_int64), ("Skv", C.c_int64), ("D", C.c_int64),
+                ("q", C.c_void_p), ("q_stride", c_i64x3),
+                ("qq", QfaQuantTensor), ("k", QfaQuantTensor), ("v", QfaQuantTensor),
+                ("d_o", C.c_void_p), ("do_stride", c_i64x3),
+                ("lse", C.c_void_p), ("delta", C.c_void_p), ("lse_stride", C.c_int64),
+                ("dq", C.c_void_p), ("dq_stride", c_i64x3),
+                ("dk", C.c_void_p), ("dk_stride", c_i64x3),
+                ("dv", C.c_void_p), ("dv_stride", c_i64x3),
+                ("dq_accum", C.c_void_p), ("status", C.c_void_p)]
+
+
+# name -> (restype, argtypes); every symbol include/qfa.h declares
+_I64 = C.c_int64
+SIGNATURES = {
+    "qfa_quant_per_token": (C.c_int, [C.c_void_p] * 5 + [_I64] * 8 + [C.c_int, C.c_void_p]),
+    "qfa_quant_dequant_per_token": (C.c_int, [C.c_void_p] * 6 + [_I64] * 8 + [C.c_int, C.c_void_p]),
+    "qfa_attn_fwd": (C.c_int, [C.POINTER(QfaFwdArgs), C.c_void_p]),
+    "qfa_attn_bwd_delta": (C.c_int, [C.c_void_p, C.POINTER(c_i64x3), C.c_void_p, C.POINTER(c_i64x3), C.c_void_p,
+                                     _I64, _I64, _I64, _I64, _I64, C.c_int, C.c_void_p]),
+    "qfa_attn_bwd": (C.c_int, [C.POINTER(QfaBwdArgs), C.c_void_p]),
+    "qfa_strerror": (C.c_char_p, [C.c_int]),
+    "qfa_last_cuda_error": (C.c_char_p, []),
+    "qfa_version": (C.c_int, []),
+    "qfa_launch_count": (C.c_int64, []),
+}
+
+_lib = None
+_lock = threading.Lock()
+
+
+def load():
+    """Loads the shared library once; raises RuntimeError with build instructions if absent."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} not found: the CUDA library is required (there is no CPU or PyTorch fallback). "
+                "Build it with `python -m quant_flash_attn_b200.build`.")
+        lib = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)  # AttributeError if the export is missing
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib
+
+
+def check(rc: int, what: str):
+    if rc != 0:
+        lib = load()
+        msg = lib.qfa_strerror(rc).decode()
+        if rc == -8:
+            msg += ": " + lib.qfa_last_cuda_error().decode()
+        raise RuntimeError(f"{what} failed: {msg} (code {rc})")
+
+
+def launch_count() -> int:
+    return int(load().qfa_launch_count())

@@ -1,0 +1,72 @@
+"""Per-token asymmetric INT8 quantization (host side).
+
+Mirrors the reference module asymmetric_quant.py: same function name, argument and
+return convention (asymmetric_quant.py:109-149); the work is done by the CUDA kernel
+behind qfa_quant_per_token.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+_DT = {torch.float16: _lib.QFA_F16, torch.bfloat16: _lib.QFA_BF16}
+
+
+def _require_cuda(t: torch.Tensor, name: str):
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor: this package has no CPU path")
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _quantize(x: torch.Tensor, want_sum: bool, want_dequant: bool):
+    if x.dim() != 4:
+        raise ValueError("expected a 4-D tensor (Batch, Num_Heads, Seq_Len, Head_Dim)")
+    _require_cuda(x, "input_tensor")
+    if x.dtype not in _DT:
+        raise TypeError(f"expected float16 or bfloat16 input, got {x.dtype}")
+    Z, H, M, K = x.shape
+    # codes are written with the input's strides (asymmetric_quant.py:64,127)
+    codes = torch.empty_like(x, dtype=torch.int8)
+    if codes.stride() != x.stride():
+        x = x.contiguous()
+        codes = torch.empty_like(x, dtype=torch.int8)
+    scale = torch.empty(Z, H, M, 1, dtype=torch.float16, device=x.device)
+    zp = torch.empty(Z, H, M, 1, dtype=torch.int8, device=x.device)
+    rowsum = torch.empty(Z, H, M, dtype=torch.int32, device=x.device) if want_sum else None
+    xhat = torch.empty(Z, H, M, K, dtype=x.dtype, device=x.device) if want_dequant else None
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        rc = lib.qfa_quant_dequant_per_token(
+            x.data_ptr(), codes.data_ptr(), scale.data_ptr(), zp.data_ptr(),
+            rowsum.data_ptr() if want_sum else None, xhat.data_ptr() if want_dequant else None,
+            Z, H, M, K, x.stride(0), x.stride(1), x.stride(2), x.stride(3), _DT[x.dtype], _stream(x))
+    _lib.check(rc, "qfa_quant_dequant_per_token")
+    return codes, scale, zp, rowsum, xhat
+
+
+def asymmetric_quant_per_token(input_tensor: torch.Tensor):
+    """Quantizes a (Batch, Num_Heads, Seq_Len, Head_Dim) fp16/bf16 CUDA tensor to INT8, one
+    scale and zero-point per token.
+
+    Returns (quantized int8 tensor with the input's shape and strides,
+             scale float16 (B,H,S,1), zero_point int8 (B,H,S,1)) -- asymmetric_quant.py:117-121.
+    """
+    codes, scale, zp, _, _ = _quantize(input_tensor, False, False)
+    return codes, scale, zp
+
+
+def asymmetric_quant_per_token_ex(input_tensor: torch.Tensor, dequant: bool = False):
+    """Same quantizer, also returning the per-token sum of the codes (int32, (B,H,S)) that the
+    int8 attention needs, and optionally the dequantized tensor (code - zp) * scale in the
+    input dtype.  Returns (codes, scale, zero_point, rowsum[, dequantized])."""
+    codes, scale, zp, rowsum, xhat = _quantize(input_tensor, True, dequant)
+    return (codes, scale, zp, rowsum, xhat) if dequant else (codes, scale, zp, rowsum)
+
+
+def dequantize_per_token(quantized_tensor, scale, zero_point):
+    """(code - zp) * scale in fp32, as the reference's helper (asymmetric_quant.py:158-160)."""
+    return (quantized_tensor.to(torch.float32) - zero_point.to(torch.float32)) * scale.to(torch.float32)

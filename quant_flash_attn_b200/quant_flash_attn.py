@@ -1,0 +1,221 @@
+"""Quantized flash attention operators (host side).
+
+`QuantFlashAttention` / `quant_flash_attn` keep the reference's signature and autograd
+contract (quant_flash_attn.py:173-240): `quant_flash_attn(q, kv_fp16, kv_quant, sm_scale)`,
+positional only, `kv_fp16` is a gradient placeholder whose values are never read, backward
+returns `(dq, dkv, None, None)` with `dkv = dV + sm_scale * dK`.
+
+`QuantAttention` / `quant_attention(q, k, v, causal, sm_scale)` is the int8 x int8 operator
+with the signature of flash_attn_triton.py:441: it quantizes q, k and v per token itself and
+returns gradients `(dq, dk, dv, None, None)` (flash_attn_triton.py:517).
+
+Both run only on CUDA through libqfa_sm100a.so; tensors are allocated here with torch and
+handed to the library as raw pointers.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+from .asymmetric_quant import _DT, _require_cuda, _stream, _quantize
+
+
+def _next_power_of_2(n: int) -> int:
+    return 1 if n <= 1 else 1 << (n - 1).bit_length()
+
+
+def _s3(t: torch.Tensor):
+    return _lib.c_i64x3(t.stride(0), t.stride(1), t.stride(2))
+
+
+def _rows16(t: torch.Tensor) -> torch.Tensor:
+    """Kernels read rows with 16-byte vectors: inner stride 1, other strides multiples of 16 bytes."""
+    m = 16 // t.element_size()
+    if t.stride(3) != 1 or any(t.stride(i) % m for i in range(3)) or t.data_ptr() % 16:
+        return t.contiguous()
+    return t
+
+
+def _flat(t: torch.Tensor) -> torch.Tensor:
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def _quant_tensor(codes, scale, zp, rowsum=None) -> _lib.QfaQuantTensor:
+    return _lib.QfaQuantTensor(codes.data_ptr(), _s3(codes), scale.data_ptr(), zp.data_ptr(),
+                               rowsum.data_ptr() if rowsum is not None else None)
+
+
+def _check_head_dim(D: int):
+    if D not in (64, 128):
+        raise ValueError(f"head dimension {D} is not supported (64 or 128)")
+
+
+class QuantFlashAttention(torch.autograd.Function):
+    """Attention of 16-bit queries against one per-token INT8-quantized tensor used as both K and V."""
+
+    @staticmethod
+    def forward(ctx, q, kv_fp16, kv_quant, sm_scale):
+        _require_cuda(q, "q")
+        Z, H, N_CTX_Q, HEAD_DIM = q.shape
+        _, _, N_CTX_KV, _ = kv_fp16.shape                      # only the shape is read (quant_flash_attn.py:181)
+        if q.dtype not in _DT:
+            raise TypeError(f"q must be float16 or bfloat16, got {q.dtype}")
+        _check_head_dim(HEAD_DIM)
+        kv_codes, kv_scale, kv_zero_point = kv_quant[:3]
+        if kv_codes.shape[2] != N_CTX_KV:
+            raise ValueError("kv_fp16 and kv_quant disagree on the KV length")
+        PADDED_N_CTX_Q = max(_next_power_of_2(N_CTX_Q), 16)   # LSE layout of quant_flash_attn.py:182,185
+        qk = _rows16(q)
+        kv_codes_k = _rows16(kv_codes)
+        kv_scale_k, kv_zp_k = _flat(kv_scale), _flat(kv_zero_point)
+        o = torch.empty_like(qk)
+        lse = torch.empty((Z, H, PADDED_N_CTX_Q), device=q.device, dtype=torch.float32)
+
+        kvq = _quant_tensor(kv_codes_k, kv_scale_k, kv_zp_k)
+        args = _lib.QfaFwdArgs(
+            mode=_lib.QFA_MODE_REF, dtype=_DT[q.dtype], causal=0, sm_scale=float(sm_scale),
+            B=Z, H=H, Sq=N_CTX_Q, Skv=N_CTX_KV, D=HEAD_DIM,
+            q=qk.data_ptr(), q_stride=_s3(qk), k=kvq, v=kvq, v_hat=None,
+            o=o.data_ptr(), o_stride=_s3(o), lse=lse.data_ptr(), lse_stride=PADDED_N_CTX_Q, status=None)
+        with torch.cuda.device(q.device):
+            rc = _lib.load().qfa_attn_fwd(C.byref(args), _stream(q))
+        _lib.check(rc, "qfa_attn_fwd")
+
+        ctx.save_for_backward(qk, o, lse, kv_codes_k, kv_scale_k, kv_zp_k)
+        ctx.sm_scale = sm_scale
+        ctx.Z, ctx.H, ctx.N_CTX_Q, ctx.HEAD_DIM = Z, H, N_CTX_Q, HEAD_DIM
+        ctx.PADDED_N_CTX_Q = PADDED_N_CTX_Q
+        return o
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        q, o, lse, kv_codes, kv_scale, kv_zero_point = ctx.saved_tensors
+        Z, H, N_CTX_Q, HEAD_DIM = ctx.Z, ctx.H, ctx.N_CTX_Q, ctx.HEAD_DIM
+        N_CTX_KV = kv_codes.shape[2]
+        do = _rows16(grad_output)
+        dq = torch.empty_like(q)
+        dkv = torch.empty(kv_codes.shape, dtype=q.dtype, device=q.device)
+        delta = torch.empty_like(lse)
+        dq_accum = torch.empty((Z, H, N_CTX_Q, HEAD_DIM), dtype=torch.float32, device=q.device)
+        lib = _lib.load()
+        stream = _stream(q)
+        with torch.cuda.device(q.device):
+            so, sdo = _s3(o), _s3(do)
+            rc = lib.qfa_attn_bwd_delta(o.data_ptr(), C.byref(so), do.data_ptr(), C.byref(sdo), delta.data_ptr(),
+                                        ctx.PADDED_N_CTX_Q, Z, H, N_CTX_Q, HEAD_DIM, _DT[q.dtype], stream)
+            _lib.check(rc, "qfa_attn_bwd_delta")
+            kvq = _quant_tensor(kv_codes, kv_scale, kv_zero_point)
+            args = _lib.QfaBwdArgs(
+                mode=_lib.QFA_MODE_REF, dtype=_DT[q.dtype], causal=0, dkv_fused=1, sm_scale=float(ctx.sm_scale),
+                B=Z, H=H, Sq=N_CTX_Q, Skv=N_CTX_KV, D=HEAD_DIM,
+                q=q.data_ptr(), q_stride=_s3(q), k=kvq, v=kvq,
+                d_o=do.data_ptr(), do_stride=sdo, lse=lse.data_ptr(), delta=delta.data_ptr(),
+                lse_stride=ctx.PADDED_N_CTX_Q,
+                dq=dq.data_ptr(), dq_stride=_s3(dq), dk=dkv.data_ptr(), dk_stride=_s3(dkv),
+                dv=None, dv_stride=_lib.c_i64x3(0, 0, 0), dq_accum=dq_accum.data_ptr(), status=None)
+            rc = lib.qfa_attn_bwd(C.byref(args), stream)
+        _lib.check(rc, "qfa_attn_bwd")
+        return dq, dkv, None, None
+
+
+quant_flash_attn = QuantFlashAttention.apply
+
+
+def quantize_qkv(q, k, v):
+    """Per-token quantization of the three operands of `quant_attention`.
+
+    Returns three tuples (codes, scale, zp, rowsum, dequantized-or-None); only V carries the
+    dequantized 16-bit tensor (the P.V operand, quant_flash_attn.py:65-66)."""
+    return _quantize(q, True, False), _quantize(k, True, False), _quantize(v, True, True)
+
+
+def int8_attention_forward(qq, kq, vq, causal: bool, sm_scale: float, dtype: torch.dtype,
+                           o: torch.Tensor | None = None, lse: torch.Tensor | None = None):
+    """Forward of the int8 operator on already quantized operands (tuples from `quantize_qkv`).
+    Returns (o, lse); lse is (B,H,Sq) fp32 natural-log."""
+    qc, qs, qz, qsum = qq[:4]
+    kc, ks, kz, ksum = kq[:4]
+    vc, vs, vz = vq[:3]
+    vhat = vq[4] if len(vq) > 4 else None
+    B, H, Sq, D = qc.shape
+    Skv = kc.shape[2]
+    _check_head_dim(D)
+    if o is None:
+        o = torch.empty((B, H, Sq, D), dtype=dtype, device=qc.device)
+    if lse is None:
+        lse = torch.empty((B, H, Sq), dtype=torch.float32, device=qc.device)
+    args = _lib.QfaFwdArgs(
+        mode=_lib.QFA_MODE_INT8, dtype=_DT[dtype], causal=int(bool(causal)), sm_scale=float(sm_scale),
+        B=B, H=H, Sq=Sq, Skv=Skv, D=D, q=None, q_stride=_lib.c_i64x3(0, 0, 0),
+        qq=_quant_tensor(qc, qs, qz, qsum), k=_quant_tensor(kc, ks, kz, ksum), v=_quant_tensor(vc, vs, vz),
+        v_hat=vhat.data_ptr() if vhat is not None else None,
+        o=o.data_ptr(), o_stride=_s3(o), lse=lse.data_ptr(), lse_stride=Sq, status=None)
+    with torch.cuda.device(qc.device):
+        rc = _lib.load().qfa_attn_fwd(C.byref(args), _stream(qc))
+    _lib.check(rc, "qfa_attn_fwd")
+    return o, lse
+
+
+def int8_attention_backward(qq, kq, vq, causal, sm_scale, o, lse, do):
+    """Backward of the int8 operator; returns (dq, dk, dv) in o's dtype."""
+    qc, qs, qz, qsum = qq[:4]
+    kc, ks, kz, ksum = kq[:4]
+    vc, vs, vz = vq[:3]
+    B, H, Sq, D = qc.shape
+    Skv = kc.shape[2]
+    dev, dtype = qc.device, o.dtype
+    do = _rows16(do)
+    dq = torch.empty((B, H, Sq, D), dtype=dtype, device=dev)
+    dk = torch.empty((B, H, Skv, D), dtype=dtype, device=dev)
+    dv = torch.empty((B, H, Skv, D), dtype=dtype, device=dev)
+    delta = torch.empty((B, H, Sq), dtype=torch.float32, device=dev)
+    dq_accum = torch.empty((B, H, Sq, D), dtype=torch.float32, device=dev)
+    lib = _lib.load()
+    stream = _stream(qc)
+    with torch.cuda.device(dev):
+        so, sdo = _s3(o), _s3(do)
+        rc = lib.qfa_attn_bwd_delta(o.data_ptr(), C.byref(so), do.data_ptr(), C.byref(sdo), delta.data_ptr(),
+                                    Sq, B, H, Sq, D, _DT[dtype], stream)
+        _lib.check(rc, "qfa_attn_bwd_delta")
+        args = _lib.QfaBwdArgs(
+            mode=_lib.QFA_MODE_INT8, dtype=_DT[dtype], causal=int(bool(causal)), dkv_fused=0,
+            sm_scale=float(sm_scale), B=B, H=H, Sq=Sq, Skv=Skv, D=D, q=None, q_stride=_lib.c_i64x3(0, 0, 0),
+            qq=_quant_tensor(qc, qs, qz, qsum), k=_quant_tensor(kc, ks, kz, ksum), v=_quant_tensor(vc, vs, vz),
+            d_o=do.data_ptr(), do_stride=sdo, lse=lse.data_ptr(), delta=delta.data_ptr(), lse_stride=Sq,
+            dq=dq.data_ptr(), dq_stride=_s3(dq), dk=dk.data_ptr(), dk_stride=_s3(dk),
+            dv=dv.data_ptr(), dv_stride=_s3(dv), dq_accum=dq_accum.data_ptr(), status=None)
+        rc = lib.qfa_attn_bwd(C.byref(args), stream)
+    _lib.check(rc, "qfa_attn_bwd")
+    return dq, dk, dv
+
+
+class QuantAttention(torch.autograd.Function):
+    """softmax(Q^ K^^T * sm_scale [causal]) V^ with Q, K, V quantized per token to INT8; the logits
+    come from an int8 x int8 tensor-core product plus zero-point corrections."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, causal, sm_scale):
+        for name, t in (("q", q), ("k", k), ("v", v)):
+            _require_cuda(t, name)
+            if t.dtype != q.dtype or t.dtype not in _DT:
+                raise TypeError("q, k, v must share dtype float16 or bfloat16")
+        if k.shape != v.shape or q.shape[:2] != k.shape[:2] or q.shape[3] != k.shape[3]:
+            raise ValueError("expected q (B,H,Sq,D) and k, v (B,H,Skv,D)")
+        qq, kq, vq = quantize_qkv(q, k, v)
+        o, lse = int8_attention_forward(qq, kq, vq, causal, sm_scale, q.dtype)
+        ctx.save_for_backward(o, lse, *qq[:4], *kq[:4], *vq[:3])
+        ctx.causal, ctx.sm_scale = bool(causal), float(sm_scale)
+        return o
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        t = ctx.saved_tensors
+        o, lse = t[0], t[1]
+        qq, kq, vq = t[2:6], t[6:10], t[10:13]
+        dq, dk, dv = int8_attention_backward(qq, kq, vq, ctx.causal, ctx.sm_scale, o, lse, grad_output)
+        return dq, dk, dv, None, None
+
+
+quant_attention = QuantAttention.apply

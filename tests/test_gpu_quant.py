@@ -1,0 +1,156 @@
+"""CUDA quantizer against the golden fixtures and the CPU oracle (through the C ABI)."""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle.quantizer import quantize_per_token
+
+pytestmark = pytest.mark.gpu
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+QUANT_CASES = sorted(glob.glob(os.path.join(HERE, "golden", "q_*.npz")))
+GPU_CASES = sorted(glob.glob(os.path.join(HERE, "golden", "gpuref_q_*.npz")))
+
+
+@pytest.fixture(scope="module")
+def qfa():
+    import quant_flash_attn_b200 as m
+    from quant_flash_attn_b200 import _lib
+    _lib.load()
+    return m
+
+
+def _compare_with_ieee_oracle(x_cpu_f32, codes, scale, zp, rowsum=None):
+    """CPU oracle divides with IEEE fp32, the GPU with div.full.f32 (<= 2 ulp): allow one code
+    on a tiny fraction of elements, never more."""
+    oc, _s32, os16, ozp, orow = quantize_per_token(x_cpu_f32)
+    codes, zp = codes.cpu().numpy(), zp.cpu().numpy().reshape(ozp.shape)
+    scale_bits = scale.cpu().numpy().reshape(os16.shape).view(np.uint16).astype(np.int32)
+    d = np.abs(codes.astype(np.int32) - oc.astype(np.int32))
+    assert d.max() <= 1
+    assert (d != 0).mean() <= 1e-4 + 4.0 / d.size
+    dz = np.abs(zp.astype(np.int32) - ozp.astype(np.int32))
+    assert dz.max() <= 1 and (dz != 0).mean() <= 1e-3 + 2.0 / dz.size
+    ds = np.abs(scale_bits - os16.view(np.uint16).astype(np.int32))
+    assert ds.max() <= 1 and (ds != 0).mean() <= 1e-3 + 2.0 / ds.size
+    if rowsum is not None:
+        assert np.array_equal(rowsum.cpu().numpy(), codes.astype(np.int64).sum(-1))
+    return int((d != 0).sum()), int((dz != 0).sum()), int((ds != 0).sum())
+
+
+@pytest.mark.parametrize("path", QUANT_CASES, ids=[os.path.basename(p)[:-4] for p in QUANT_CASES])
+def test_quantizer_vs_reference_fixtures(qfa, path):
+    g = np.load(path)
+    # rebuild the fixture's strided view (one case is (B,S,H,D) data seen as (B,H,S,D))
+    base = torch.empty(g["x"].size, dtype=torch.float16, device="cuda")
+    x = torch.as_strided(base, tuple(g["x"].shape), [int(s) for s in g["x_stride"]])
+    x.copy_(torch.from_numpy(g["x"]).cuda())
+    codes, scale, zp, rowsum = qfa.asymmetric_quant_per_token_ex(x)
+    assert codes.stride() == x.stride()
+    assert scale.shape == (*x.shape[:3], 1) and scale.dtype == torch.float16 and zp.dtype == torch.int8
+    # the fixtures come from the reference kernels run with IEEE division (CPU interpreter)
+    dc = (codes.cpu().numpy().astype(np.int32) - g["codes"].astype(np.int32))
+    assert np.abs(dc).max() <= 1 and (dc != 0).sum() <= 2
+    assert np.abs(zp.cpu().numpy().astype(np.int32) - g["zp"].astype(np.int32)).max() <= 1
+    assert np.abs(scale.cpu().numpy().view(np.uint16).astype(np.int32) -
+                  g["scale"].view(np.uint16).astype(np.int32)).max() <= 1
+    assert np.array_equal(rowsum.cpu().numpy(), codes.cpu().numpy().astype(np.int64).sum(-1))
+
+
+@pytest.mark.parametrize("path", GPU_CASES, ids=[os.path.basename(p)[:-4] for p in GPU_CASES])
+def test_quantizer_bit_exact_vs_reference_on_gpu(qfa, path):
+    """Fixtures written by the reference's Triton kernel on a B200: equality must be exact."""
+    g = np.load(path)
+    dt = torch.bfloat16 if str(g["dtype"]) == "bfloat16" else torch.float16
+    x = torch.from_numpy(g["x_bits"]).cuda().view(dt)
+    codes, scale, zp = qfa.asymmetric_quant_per_token(x)
+    assert np.array_equal(codes.cpu().numpy(), g["codes"])
+    assert np.array_equal(scale.cpu().numpy().view(np.uint16), g["scale"].view(np.uint16))
+    assert np.array_equal(zp.cpu().numpy(), g["zp"])
+
+
+def _inputs(kind, shape, dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(shape, generator=g)
+    if kind == "outlier":
+        D = shape[-1]
+        idx = torch.randperm(D, generator=g)[: max(1, (D + 99) // 100)]
+        x[..., idx] *= 20.0
+    elif kind == "loguniform":
+        mag = torch.exp(torch.empty(shape[:-1] + (1,)).uniform_(np.log(0.1), np.log(10.0), generator=g))
+        x = x * mag
+    return x.to(dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("kind,shape", [
+    ("normal", (1, 4, 512, 64)), ("normal", (2, 8, 1023, 128)), ("outlier", (2, 3, 257, 128)),
+    ("loguniform", (1, 2, 999, 128)), ("normal", (1, 1, 1, 64)), ("normal", (3, 2, 65, 256)),
+    ("normal", (1, 2, 33, 8)), ("normal", (2, 2, 40, 32)), ("normal", (1, 3, 50, 96)),
+    ("normal", (1, 2, 31, 40)), ("normal", (1, 1, 7, 1)),
+])
+def test_quantizer_vs_oracle(qfa, dtype, kind, shape):
+    x = _inputs(kind, shape, dtype, seed=sum(shape) + len(kind))
+    codes, scale, zp, rowsum, xhat = qfa.asymmetric_quant_per_token_ex(x.cuda(), dequant=True)
+    _compare_with_ieee_oracle(x.float().numpy(), codes, scale, zp, rowsum)
+    want = ((codes.float() - zp.float()) * scale.float()).to(dtype)
+    assert torch.equal(xhat, want)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_quantizer_strided_inputs(qfa, dtype):
+    # (B,S,H,D)-contiguous data viewed as (B,H,S,D) -- codes must inherit the strides
+    base = _inputs("normal", (2, 37, 5, 128), dtype, 3).cuda()
+    x = base.transpose(1, 2)
+    codes, scale, zp = qfa.asymmetric_quant_per_token(x)
+    assert codes.stride() == x.stride()
+    c2, s2, z2 = qfa.asymmetric_quant_per_token(x.contiguous())
+    assert torch.equal(codes, c2) and torch.equal(scale, s2) and torch.equal(zp, z2)
+    # inner stride != 1 goes through the general kernel
+    y = _inputs("normal", (1, 2, 19, 128), dtype, 4).cuda()[..., ::2]
+    c3, s3, z3 = qfa.asymmetric_quant_per_token(y)
+    c4, s4, z4 = qfa.asymmetric_quant_per_token(y.contiguous())
+    assert torch.equal(c3, c4) and torch.equal(s3, s4) and torch.equal(z3, z4)
+
+
+def test_quantizer_edge_rows(qfa):
+    D = 128
+    rows = torch.stack([
+        torch.zeros(D), torch.full((D,), -7.5), torch.linspace(0, 255, D), torch.linspace(-127.5, 127.5, D),
+        torch.cat([torch.full((D - 1,), float("nan")), torch.tensor([1.0])]),
+        torch.cat([torch.ones(D - 1), torch.tensor([float("inf")])]),
+    ]).to(torch.bfloat16)[None, None].cuda()
+    codes, scale, zp, rowsum = qfa.asymmetric_quant_per_token_ex(rows)
+    torch.cuda.synchronize()
+    assert scale[0, 0, 0, 0] == 1.0 and zp[0, 0, 0, 0] == -128 and (codes[0, 0, 0] == -128).all()
+    assert scale[0, 0, 1, 0] == 1.0 and (codes[0, 0, 1] == -128).all()      # -128 + 7.5 - 7.5 -> clamp
+    oc, _, os16, ozp, _ = quantize_per_token(rows[0, 0, :4].float().cpu().numpy())
+    assert np.array_equal(codes[0, 0, :4].cpu().numpy(), oc)
+    assert np.array_equal(rowsum.cpu().numpy(), codes.cpu().numpy().astype(np.int64).sum(-1))
+
+
+def test_quantizer_is_idempotent_on_its_own_output(qfa):
+    """Size-independent property at a full benchmark size: quantizing the dequantized tensor
+    reproduces codes whose dequantization is (nearly) a fixed point, and row sums match."""
+    x = torch.randn(4, 32, 4096, 128, device="cuda", dtype=torch.bfloat16)
+    codes, scale, zp, rowsum = qfa.asymmetric_quant_per_token_ex(x)
+    assert int(codes.min()) == -128 and int(codes.max()) == 127
+    assert torch.equal(rowsum, codes.sum(-1, dtype=torch.int32))
+    xh = (codes.float() - zp.float()) * scale.float()
+    err = (xh - x.float()).abs()
+    assert bool((err <= 0.51 * scale.float() + 0.01 * x.float().abs()).all())
+
+
+def test_quantizer_rejects_bad_arguments(qfa):
+    with pytest.raises(RuntimeError):
+        qfa.asymmetric_quant_per_token(torch.zeros(1, 1, 2, 64, dtype=torch.float16))       # CPU tensor
+    with pytest.raises(TypeError):
+        qfa.asymmetric_quant_per_token(torch.zeros(1, 1, 2, 64, device="cuda"))             # fp32
+    with pytest.raises(ValueError):
+        qfa.asymmetric_quant_per_token(torch.zeros(2, 64, device="cuda", dtype=torch.float16))
+    # empty input is a no-op
+    c, s, z = qfa.asymmetric_quant_per_token(torch.zeros(1, 2, 0, 64, device="cuda", dtype=torch.float16))
+    assert c.numel() == 0 and s.numel() == 0

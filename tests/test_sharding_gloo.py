@@ -1,0 +1,52 @@
+"""World-size-2 check (gloo, CPU) of the multi-GPU plan: ranks take disjoint contiguous slices of
+the (batch x head) axis, compute independently, and the union of their results equals the
+single-process result.  The per-head computation here is the CPU oracle standing in for the
+kernel; what is tested is the partition and the absence of any exchange on the data path."""
+import os
+import socket
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import oracle
+    from quant_flash_attn_b200 import head_slice, shard_bounds
+    torch.manual_seed(0)
+    B, H, S, D = 2, 3, 64, 64
+    q, k, v = (torch.randn(B, H, S, D).bfloat16() for _ in range(3))
+    s, e = shard_bounds(B * H, world, rank)
+    ql, kl, vl = (head_slice(t, world, rank) for t in (q, k, v))
+    assert ql.shape == (1, e - s, S, D)
+    o, lse, _ = oracle.int8_mode_forward(ql, kl, vl, True, 0.125)
+    # timing protocol of the benchmark: barrier, then max over ranks of the local time
+    t = torch.tensor([float(rank + 1)])
+    dist.barrier()
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    assert t.item() == world
+    torch.save({"span": (s, e), "o": o, "lse": lse}, os.path.join(out_dir, f"r{rank}.pt"))
+    dist.destroy_process_group()
+
+
+def test_two_rank_head_partition_matches_single_process(tmp_path):
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    import oracle
+    torch.manual_seed(0)
+    B, H, S, D = 2, 3, 64, 64
+    q, k, v = (torch.randn(B, H, S, D).bfloat16() for _ in range(3))
+    o_full, lse_full, _ = oracle.int8_mode_forward(q, k, v, True, 0.125)
+    parts = [torch.load(os.path.join(tmp_path, f"r{r}.pt")) for r in range(world)]
+    assert parts[0]["span"][0] == 0 and parts[-1]["span"][1] == B * H
+    o = torch.cat([p["o"] for p in parts], dim=1).reshape(B, H, S, D)
+    lse = torch.cat([p["lse"] for p in parts], dim=1).reshape(B, H, S)
+    assert torch.equal(o, o_full) and torch.equal(lse, lse_full)
