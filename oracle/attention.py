@@ -57,9 +57,10 @@ def _quantize_t(x: torch.Tensor):
 
 # --------------------------------------------------------------------------- ref mode
 
-def ref_mode_forward(q, codes, scale_f16, zp, sm_scale, compute=torch.float32):
+def ref_mode_forward(q, codes, scale_f16, zp, sm_scale, compute=torch.float32, round_output=True):
     """q (Z,H,NQ,D) fp16/bf16; codes (Z,H,NKV,D) int8; scale/zp (Z,H,NKV,1).
-    Returns O (q dtype) and LSE (Z,H,NQ) fp32.  quant_flash_attn.py:50-83."""
+    Returns O (q dtype, or un-rounded when round_output is False) and LSE (Z,H,NQ) fp32.
+    quant_flash_attn.py:50-83."""
     kv = _dequant_t(codes, scale_f16, zp).to(q.dtype)                      # :65-66
     qs = (q.float() * sm_scale).to(q.dtype)                               # :52 (fp32 product, rounded)
     s = qs.to(compute) @ kv.to(compute).transpose(-1, -2)                  # :68
@@ -68,11 +69,12 @@ def ref_mode_forward(q, codes, scale_f16, zp, sm_scale, compute=torch.float32):
     l = p.sum(dim=-1, keepdim=True)
     o = (p @ kv.to(compute)) / l                                           # :75-78
     lse = (m + torch.log(l)).squeeze(-1)                                   # :79
-    return o.to(q.dtype), lse.float()
+    return (o.to(q.dtype) if round_output else o), lse.float()
 
 
-def ref_mode_backward(q, codes, scale_f16, zp, sm_scale, o, lse, do, compute=torch.float32):
-    """Returns (dq, dkv) in q's dtype.  quant_flash_attn.py:88-101 and :133-166."""
+def ref_mode_backward(q, codes, scale_f16, zp, sm_scale, o, lse, do, compute=torch.float32, round_output=True):
+    """Returns (dq, dkv) in q's dtype (un-rounded when round_output is False).
+    quant_flash_attn.py:88-101 and :133-166."""
     kv = _dequant_t(codes, scale_f16, zp).to(q.dtype).to(compute)          # :150-151
     delta = (o.to(compute) * do.to(compute)).sum(-1, keepdim=True)         # :99
     qf, dof = q.to(compute), do.to(compute)
@@ -84,7 +86,7 @@ def ref_mode_backward(q, codes, scale_f16, zp, sm_scale, o, lse, do, compute=tor
     dq = (ds @ kv) * sm_scale                                              # :159,164
     dk = ds.transpose(-1, -2) @ qf                                         # :160
     dkv = dv + dk * sm_scale                                               # :161
-    return dq.to(q.dtype), dkv.to(q.dtype)
+    return (dq.to(q.dtype), dkv.to(q.dtype)) if round_output else (dq, dkv)
 
 
 # --------------------------------------------------------------------------- int8 mode
@@ -113,10 +115,18 @@ def int8_mode_quantize(x):
     return _quantize_t(x)
 
 
-def int8_mode_forward(q, k, v, causal, sm_scale, compute=torch.float32):
+def int8_mode_forward(q, k, v, causal, sm_scale, compute=torch.float32, quant=None, round_output=True):
     """q,k,v (B,H,S,D) 16-bit.  Returns O (q dtype), LSE (B,H,Sq) fp32 and the
-    quantized operands (for the backward)."""
-    qq, kq, vq = _quantize_t(q), _quantize_t(k), _quantize_t(v)
+    quantized operands (for the backward).
+
+    `quant` = ((codes, scale, zp, rowsum),)*3 for q, k, v overrides the CPU quantizer, so
+    that attention can be judged on exactly the operands a GPU quantizer produced (GPU
+    division is not IEEE, see quantizer.py); scale is the fp32 value of the stored fp16
+    scale, shapes (B,H,S)."""
+    if quant is None:
+        qq, kq, vq = _quantize_t(q), _quantize_t(k), _quantize_t(v)
+    else:
+        qq, kq, vq = quant
     s = int8_mode_logits(qq, kq, sm_scale, causal, compute)
     m = s.max(dim=-1, keepdim=True).values
     p = torch.exp(s - m)
@@ -124,12 +134,12 @@ def int8_mode_forward(q, k, v, causal, sm_scale, compute=torch.float32):
     vhat = _dequant_t(vq[0], vq[1].unsqueeze(-1), vq[2].unsqueeze(-1)).to(q.dtype).to(compute)
     o = (p @ vhat) / l
     lse = (m + torch.log(l)).squeeze(-1)
-    return o.to(q.dtype), lse.float(), (qq, kq, vq)
+    return (o.to(q.dtype) if round_output else o), lse.float(), (qq, kq, vq)
 
 
-def int8_mode_backward(quant, causal, sm_scale, o, lse, do, dtype, compute=torch.float32):
+def int8_mode_backward(quant, causal, sm_scale, o, lse, do, dtype, compute=torch.float32, round_output=True):
     """Gradients of int8_mode_forward w.r.t. the dequantized operands
-    (straight-through): returns dq, dk, dv in `dtype`."""
+    (straight-through): returns dq, dk, dv in `dtype` (un-rounded when round_output is False)."""
     qq, kq, vq = quant
     s = int8_mode_logits(qq, kq, sm_scale, causal, compute)
     p = torch.exp(s - lse.to(compute).unsqueeze(-1))
@@ -143,7 +153,7 @@ def int8_mode_backward(quant, causal, sm_scale, o, lse, do, dtype, compute=torch
     ds = p * (dp - delta)
     dq = (ds @ khat) * sm_scale
     dk = (ds.transpose(-1, -2) @ qhat) * sm_scale
-    return dq.to(dtype), dk.to(dtype), dv.to(dtype)
+    return (dq.to(dtype), dk.to(dtype), dv.to(dtype)) if round_output else (dq, dk, dv)
 
 
 def default_sm_scale(D):

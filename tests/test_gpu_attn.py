@@ -15,10 +15,14 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 ATTN_CASES = sorted(glob.glob(os.path.join(HERE, "golden", "a_*.npz")))
 
-# north-star tolerance for results that share the kernel's semantics:
-# max-abs error <= 2e-3 of the output scale, cosine similarity >= 0.9999
+# north-star tolerance for results that share the kernel's semantics: max-abs error <= 2e-3 of
+# the output scale, cosine similarity >= 0.9999.  The kernel's result is STORED in a 16-bit dtype,
+# which alone moves an element by up to half an ulp of its own magnitude (2^-8 relative for
+# bf16, 2^-11 for fp16); the comparison is against the oracle's un-rounded fp32 result and adds
+# exactly that storage term.
 REL_TOL = 2e-3
 COS_TOL = 0.9999
+HALF_ULP = {torch.bfloat16: 2.0 ** -8, torch.float16: 2.0 ** -11}
 
 
 @pytest.fixture(scope="module")
@@ -30,13 +34,21 @@ def qfa():
 
 
 def _close(got, want, rel=REL_TOL, cos=COS_TOL, what=""):
+    storage = HALF_ULP.get(got.dtype, 0.0)
     got, want = got.detach().float().cpu().flatten(), want.detach().float().cpu().flatten()
     assert torch.isfinite(got).all(), what
     scale = want.abs().max().item()
-    err = (got - want).abs().max().item()
+    excess = ((got - want).abs() - storage * want.abs()).max().item()
     c = torch.nn.functional.cosine_similarity(got.double(), want.double(), dim=0).item()
-    assert err <= rel * scale, f"{what}: max-abs {err:.3e} > {rel} * {scale:.3e}"
-    assert c >= cos, f"{what}: cosine {c}"
+    assert excess <= rel * scale + 1e-5, f"{what}: max-abs excess {excess:.3e} > {rel} * {scale:.3e}"
+    if scale > 1e-4:
+        assert c >= cos, f"{what}: cosine {c}"
+
+
+def _cpu_quant(t):
+    """GPU quantizer output tuple -> the oracle's (codes, scale fp32, zp, rowsum) on CPU."""
+    codes, scale, zp, rowsum = t[:4]
+    return (codes.cpu(), scale.float().cpu().squeeze(-1), zp.cpu().squeeze(-1), rowsum.cpu())
 
 
 def _gen(shape, dtype, seed, kind="normal"):
@@ -84,12 +96,12 @@ def test_ref_mode_vs_oracle_ragged(qfa, dtype, shape):
     o = qfa.quant_flash_attn(qc, kvc, kvq, sm)
     o.backward(go.cuda())
     codes, scale, zp = (t.cpu() for t in kvq)
-    o_ref, lse_ref = oracle.ref_mode_forward(q, codes, scale, zp, sm)
-    rel = REL_TOL if dtype == torch.float16 else 8e-3   # bf16 P / output rounding: 2^-9 per element
-    _close(o, o_ref, rel=rel, what="o")
-    dq_ref, dkv_ref = oracle.ref_mode_backward(q, codes, scale, zp, sm, o.detach().cpu(), lse_ref, go)
-    _close(qc.grad, dq_ref, rel=rel, what="dq")
-    _close(kvc.grad, dkv_ref, rel=rel, what="dkv")
+    o_ref, lse_ref = oracle.ref_mode_forward(q, codes, scale, zp, sm, round_output=False)
+    _close(o, o_ref, what="o")
+    dq_ref, dkv_ref = oracle.ref_mode_backward(q, codes, scale, zp, sm, o.detach().cpu(), lse_ref, go,
+                                               round_output=False)
+    _close(qc.grad, dq_ref, what="dq")
+    _close(kvc.grad, dkv_ref, what="dkv")
 
 
 # the reference's own accuracy test (shapes and tolerances of test_accuracy.py:35-45,115,123,131)
@@ -140,14 +152,16 @@ def test_int8_mode_forward_backward_vs_oracle(qfa, dtype, B, H, Sq, Skv, D, caus
     qc, kc, vc = (t.cuda().requires_grad_() for t in (q, k, v))
     o = qfa.quant_attention(qc, kc, vc, causal, sm)
     o.backward(do.cuda())
-    o_ref, lse_ref, quant = oracle.int8_mode_forward(q, k, v, causal, sm)
-    # bf16 carries 8 mantissa bits: P and the stored output are rounded at 2^-9 relative
-    rel = REL_TOL if dtype == torch.float16 else 6e-3
-    _close(o, o_ref, rel=rel, what="o")
-    dq_ref, dk_ref, dv_ref = oracle.int8_mode_backward(quant, causal, sm, o.detach().cpu(), lse_ref, do, dtype)
-    _close(qc.grad, dq_ref, rel=rel, what="dq")
-    _close(kc.grad, dk_ref, rel=rel, what="dk")
-    _close(vc.grad, dv_ref, rel=rel, what="dv")
+    # the oracle gets the operands exactly as the GPU quantizer produced them (the quantizer has
+    # its own bit-exact tests; CPU division would move ~0.4 % of the codes by one)
+    quant = tuple(_cpu_quant(t) for t in qfa.quantize_qkv(qc.detach(), kc.detach(), vc.detach()))
+    o_ref, lse_ref, quant = oracle.int8_mode_forward(q, k, v, causal, sm, quant=quant, round_output=False)
+    _close(o, o_ref, what="o")
+    dq_ref, dk_ref, dv_ref = oracle.int8_mode_backward(quant, causal, sm, o.detach().cpu(), lse_ref, do, dtype,
+                                                       round_output=False)
+    _close(qc.grad, dq_ref, what="dq")
+    _close(kc.grad, dk_ref, what="dk")
+    _close(vc.grad, dv_ref, what="dv")
 
 
 def test_int8_mode_lse_and_quantized_operands(qfa):
@@ -156,9 +170,10 @@ def test_int8_mode_lse_and_quantized_operands(qfa):
     qq, kq, vq = qfa.quantize_qkv(q.cuda(), k.cuda(), v.cuda())
     for causal in (False, True):
         o, lse = qfa.int8_attention_forward(qq, kq, vq, causal, 0.1, torch.bfloat16)
-        o_ref, lse_ref, _ = oracle.int8_mode_forward(q, k, v, causal, 0.1)
+        o_ref, lse_ref, _ = oracle.int8_mode_forward(q, k, v, causal, 0.1, round_output=False,
+                                                     quant=tuple(_cpu_quant(t) for t in (qq, kq, vq)))
         assert (lse.cpu() - lse_ref).abs().max() <= 2e-3
-        _close(o, o_ref, rel=6e-3, what="o")
+        _close(o, o_ref, what="o")
 
 
 def test_training_shape_properties(qfa):
