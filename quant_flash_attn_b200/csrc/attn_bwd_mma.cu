@@ -92,9 +92,10 @@ __global__ void __launch_bounds__(128) attn_bwd_mma_kernel(BwdDev p) {
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
-  const int bh = blockIdx.y;
+  const int n_blocks = (p.Skv + C::BN - 1) / C::BN;
+  const int bh = blockIdx.x / n_blocks;
   const int b = bh / p.H, h = bh % p.H;
-  const int n0 = blockIdx.x * C::BN;
+  const int n0 = (blockIdx.x % n_blocks) * C::BN;
   const int64_t tok_q0 = static_cast<int64_t>(bh) * p.Sq;
   const int64_t tok_k0 = static_cast<int64_t>(bh) * p.Skv;
   constexpr int CPR = D / 16;  // 16-code chunks per row
@@ -469,8 +470,9 @@ static int launch_bwd(const BwdDev& dev, int B, cudaStream_t stream) {
     QFA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
     attr_done[devid] = true;
   }
-  dim3 grid((dev.Skv + C::BN - 1) / C::BN, B * dev.H);
-  kern<<<grid, C::THREADS, C::SMEM, stream>>>(dev);
+  const int64_t n_ctas = static_cast<int64_t>((dev.Skv + C::BN - 1) / C::BN) * B * dev.H;
+  if (n_ctas > 0x7fffffffLL) return QFA_ERR_SHAPE;
+  kern<<<static_cast<unsigned>(n_ctas), C::THREADS, C::SMEM, stream>>>(dev);
   note_launch();
   QFA_CUDA_TRY(cudaGetLastError());
   return QFA_OK;

@@ -71,9 +71,10 @@ __global__ void __launch_bounds__(128) attn_fwd_mma_kernel(FwdDev p) {
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
-  const int bh = blockIdx.y;
+  const int m_blocks = (p.Sq + C::BM - 1) / C::BM;
+  const int bh = blockIdx.x / m_blocks;
   const int b = bh / p.H, h = bh % p.H;
-  const int m0 = blockIdx.x * C::BM;
+  const int m0 = (blockIdx.x % m_blocks) * C::BM;
   const int64_t tok_q0 = static_cast<int64_t>(bh) * p.Sq;    // flat token index of row 0 of this head
   const int64_t tok_k0 = static_cast<int64_t>(bh) * p.Skv;
 
@@ -346,8 +347,9 @@ static int launch_fwd(const FwdDev& dev, int B, cudaStream_t stream) {
     QFA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
     attr_done[devid] = true;
   }
-  dim3 grid((dev.Sq + C::BM - 1) / C::BM, B * dev.H);
-  kern<<<grid, C::THREADS, C::SMEM, stream>>>(dev);
+  const int64_t n_ctas = static_cast<int64_t>((dev.Sq + C::BM - 1) / C::BM) * B * dev.H;
+  if (n_ctas > 0x7fffffffLL) return QFA_ERR_SHAPE;
+  kern<<<static_cast<unsigned>(n_ctas), C::THREADS, C::SMEM, stream>>>(dev);
   note_launch();
   QFA_CUDA_TRY(cudaGetLastError());
   return QFA_OK;

@@ -20,7 +20,11 @@ ATTN_CASES = sorted(glob.glob(os.path.join(HERE, "golden", "a_*.npz")))
 # which alone moves an element by up to half an ulp of its own magnitude (2^-8 relative for
 # bf16, 2^-11 for fp16); the comparison is against the oracle's un-rounded fp32 result and adds
 # exactly that storage term.
+# Gradients computed from bf16 operands get twice the bound: the kernels (like the reference,
+# quant_flash_attn.py:156,159-160) round P and dS to the input dtype before the gradient
+# products, and with 8 significant bits that alone is ~3e-3 of the gradient scale; fp16 meets 2e-3.
 REL_TOL = 2e-3
+REL_TOL_GRAD = {torch.bfloat16: 4e-3, torch.float16: 2e-3}
 COS_TOL = 0.9999
 HALF_ULP = {torch.bfloat16: 2.0 ** -8, torch.float16: 2.0 ** -11}
 
@@ -100,8 +104,8 @@ def test_ref_mode_vs_oracle_ragged(qfa, dtype, shape):
     _close(o, o_ref, what="o")
     dq_ref, dkv_ref = oracle.ref_mode_backward(q, codes, scale, zp, sm, o.detach().cpu(), lse_ref, go,
                                                round_output=False)
-    _close(qc.grad, dq_ref, what="dq")
-    _close(kvc.grad, dkv_ref, what="dkv")
+    _close(qc.grad, dq_ref, rel=REL_TOL_GRAD[dtype], what="dq")
+    _close(kvc.grad, dkv_ref, rel=REL_TOL_GRAD[dtype], what="dkv")
 
 
 # the reference's own accuracy test (shapes and tolerances of test_accuracy.py:35-45,115,123,131)
@@ -159,9 +163,9 @@ def test_int8_mode_forward_backward_vs_oracle(qfa, dtype, B, H, Sq, Skv, D, caus
     _close(o, o_ref, what="o")
     dq_ref, dk_ref, dv_ref = oracle.int8_mode_backward(quant, causal, sm, o.detach().cpu(), lse_ref, do, dtype,
                                                        round_output=False)
-    _close(qc.grad, dq_ref, what="dq")
-    _close(kc.grad, dk_ref, what="dk")
-    _close(vc.grad, dv_ref, what="dv")
+    _close(qc.grad, dq_ref, rel=REL_TOL_GRAD[dtype], what="dq")
+    _close(kc.grad, dk_ref, rel=REL_TOL_GRAD[dtype], what="dk")
+    _close(vc.grad, dv_ref, rel=REL_TOL_GRAD[dtype], what="dv")
 
 
 def test_int8_mode_lse_and_quantized_operands(qfa):
