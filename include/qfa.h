@@ -157,6 +157,26 @@ typedef struct {
 
 QFA_API int qfa_attn_bwd(const QfaBwdArgs* args, qfa_stream_t stream);
 
+/* Backward without allocation.  No counterpart in the reference (its backward allocates its
+ * buffers with torch, quant_flash_attn.py:213-216); added for hosts that cannot obtain device
+ * memory at call time, e.g. an inference-engine plugin whose enqueue hook must not allocate, or a
+ * process that gave the whole device to a memory pool at start-up.
+ *
+ * Identical to qfa_attn_bwd except that `dq_accum` in `args` is ignored: the fp32 dQ accumulator
+ * is a fixed array inside the library (qfa_static_scratch_capacity() floats = 16 MiB, resident
+ * on every GPU that loads the library until the process exits).  The call allocates and frees
+ * nothing, neither through CUDA nor through any library.
+ *   - B*H*Sq*D must not exceed qfa_static_scratch_capacity(); larger problems return
+ *     QFA_ERR_TOO_LARGE before anything is launched.
+ *   - The first call on each device looks up the array's device address (the device must be
+ *     current, as for every entry point); make that first call outside any stream capture.
+ *   - All calls share the one array; the used part is zero-filled at the start of each call and
+ *     holds stale data otherwise.  Two calls whose kernels overlap on the GPU (different
+ *     streams) race on it: serialize them. */
+QFA_API int qfa_attn_bwd_static_scratch(const QfaBwdArgs* args, qfa_stream_t stream);
+/* Capacity, in floats, of the accumulator used by qfa_attn_bwd_static_scratch. */
+QFA_API int64_t qfa_static_scratch_capacity(void);
+
 /* Text for a return / status code. */
 QFA_API const char* qfa_strerror(int code);
 /* Last CUDA error string seen by this library on the calling thread ("" if none). */

@@ -55,6 +55,8 @@ SIGNATURES = {
     "qfa_attn_bwd_delta": (C.c_int, [C.c_void_p, C.POINTER(c_i64x3), C.c_void_p, C.POINTER(c_i64x3), C.c_void_p,
                                      _I64, _I64, _I64, _I64, _I64, C.c_int, C.c_void_p]),
     "qfa_attn_bwd": (C.c_int, [C.POINTER(QfaBwdArgs), C.c_void_p]),
+    "qfa_attn_bwd_static_scratch": (C.c_int, [C.POINTER(QfaBwdArgs), C.c_void_p]),
+    "qfa_static_scratch_capacity": (C.c_int64, []),
     "qfa_strerror": (C.c_char_p, [C.c_int]),
     "qfa_last_cuda_error": (C.c_char_p, []),
     "qfa_version": (C.c_int, []),
