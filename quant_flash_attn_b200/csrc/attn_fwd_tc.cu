@@ -10,9 +10,11 @@
 //
 // One CTA owns two 128-row query tiles of one (batch, head) and walks over 128-token K/V tiles.
 // Warp roles: warp 0 = TMA producer (+ per-column constants), warp 1 = MMA issuer, warp 2 = tensor
-// memory allocator, warps 4-7 / 8-11 = softmax of query tile 0 / 1 (one thread per row, so row max
-// and row sum need no shuffles).  The two query tiles ping-pong: while the softmax warps of one
-// tile work, the tensor core runs the other tile's MMAs.  O is only rescaled when the running max
+// memory allocator, warps 4-11 / 12-19 = softmax of query tile 0 / 1: two threads per row, one per
+// 64-column half, so that four softmax warps are resident per scheduler; the halves exchange the
+// row max through shared memory, no shuffles.  The element-wise math uses packed f32x2
+// instructions.  The two query tiles ping-pong: while the softmax warps of one tile work, the
+// tensor core runs the other tile's MMAs.  O is only rescaled when the running max
 // grew by more than 2^8 (the softmax threads do it in place in tensor memory), which makes the
 // rescale rare after the first tiles.
 //
@@ -49,16 +51,19 @@ struct TcCfg {
   static constexpr int V_BYTES = BN * D * 2;             // 16-bit
   static constexpr int V_PANELS = D / 64;                // 64-element (128-byte) column panels
   static constexpr int V_PANEL_BYTES = BN * 128;
-  static constexpr int M_BYTES = BN * 16;                // float4 per column
+  static constexpr int M_BYTES = BN * 12;                // per column: z_k, -sum(k), s_k as three float arrays
   static constexpr int Q_OFF = 0;
   static constexpr int K_OFF = Q_OFF + NQT * Q_BYTES;
   static constexpr int V_OFF = K_OFF + KSTAGES * K_BYTES;
   static constexpr int M_OFF = V_OFF + VSTAGES * V_BYTES;
-  static constexpr int BAR_OFF = M_OFF + MSTAGES * M_BYTES;
-  static constexpr int NBARS = 1 + 2 * KSTAGES + 2 * VSTAGES + 2 * MSTAGES + 3 * NQT;
+  static constexpr int X_OFF = M_OFF + MSTAGES * M_BYTES;   // row-max exchange between the two column halves
+  static constexpr int X_BYTES = 2 * NQT * 2 * BM * 4;      // [parity][tile][half][row] floats
+  static constexpr int BAR_OFF = X_OFF + X_BYTES;
+  static constexpr int NBARS = 1 + 2 * KSTAGES + 2 * VSTAGES + 2 * MSTAGES + 3 * NQT + 4 * NQT;
   static constexpr int MISC_OFF = BAR_OFF + NBARS * 8;
   static constexpr int SMEM = MISC_OFF + 16 + 1024;      // + slack for 1024-byte alignment of the base
-  static constexpr int THREADS = 384;
+  static constexpr int SOFTMAX_THREADS = NQT * 2 * BM;   // two threads per query row (one per column half)
+  static constexpr int THREADS = 128 + SOFTMAX_THREADS;
   // tensor memory columns
   static constexpr int S_COL = 0;                        // S_t at t*BN (int32), P_t aliases its first BN/2 columns
   static constexpr int O_COL = NQT * BN;                 // O_t at O_COL + t*D (fp32)
@@ -67,7 +72,7 @@ struct TcCfg {
 };
 
 template <typename T, int D>
-__global__ void __launch_bounds__(384, 1)
+__global__ void __launch_bounds__(640, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const TcFwdParams p) {
   using C = TcCfg<D>;
@@ -83,6 +88,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   constexpr int B_VFULL = B_KEMPTY + C::KSTAGES, B_VEMPTY = B_VFULL + C::VSTAGES;
   constexpr int B_MFULL = B_VEMPTY + C::VSTAGES, B_MEMPTY = B_MFULL + C::MSTAGES;
   constexpr int B_SFULL = B_MEMPTY + C::MSTAGES, B_PFULL = B_SFULL + C::NQT, B_ODONE = B_PFULL + C::NQT;
+  constexpr int B_PAIR = B_ODONE + C::NQT;               // [tile][lane quarter]: the two warps sharing 32 rows
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::MISC_OFF);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::MISC_OFF + 4);
 
@@ -110,11 +116,12 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     mbar_init(BAR(B_QFULL), 1);
     for (int i = 0; i < C::KSTAGES; ++i) { mbar_init(BAR(B_KFULL + i), 1); mbar_init(BAR(B_KEMPTY + i), 1); }
     for (int i = 0; i < C::VSTAGES; ++i) { mbar_init(BAR(B_VFULL + i), 1); mbar_init(BAR(B_VEMPTY + i), 1); }
-    for (int i = 0; i < C::MSTAGES; ++i) { mbar_init(BAR(B_MFULL + i), 32); mbar_init(BAR(B_MEMPTY + i), C::NQT * C::BM); }
+    for (int i = 0; i < C::MSTAGES; ++i) { mbar_init(BAR(B_MFULL + i), 32); mbar_init(BAR(B_MEMPTY + i), C::SOFTMAX_THREADS); }
     for (int t = 0; t < C::NQT; ++t) {
       mbar_init(BAR(B_SFULL + t), 1);
-      mbar_init(BAR(B_PFULL + t), C::BM);
+      mbar_init(BAR(B_PFULL + t), 2 * C::BM);
       mbar_init(BAR(B_ODONE + t), 1);
+      for (int w = 0; w < 4; ++w) mbar_init(BAR(B_PAIR + t * 4 + w), 64);
     }
     fence_barrier_init();
   }
@@ -127,6 +134,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
 
+  // the softmax warpgroups hold a whole 128-column row per thread: move registers to them
+  if (warp < 4) {
+  // control warpgroup: give registers away (the softmax warpgroups hold a whole row per thread)
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
   if (warp == 0) {
     // ================================================================ producer
     if (lane == 0) {
@@ -150,22 +161,24 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         mbar_arrive_expect_tx(BAR(B_KFULL + ks), C::K_BYTES);
         tma_load_4d(sbase + C::K_OFF + ks * C::K_BYTES, &tmK, BAR(B_KFULL + ks), 0, n0, h, b);
       }
-      // per-column constants: (s_k, z_k, -sum(k), 0)
+      // per-column constants z_k, -sum(k), s_k
       ok = mbar_wait(BAR(B_MEMPTY + ms), ((j / C::MSTAGES) & 1) ^ 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      float4* meta = reinterpret_cast<float4*>(smem + C::M_OFF + ms * C::M_BYTES);
+      float* meta = reinterpret_cast<float*>(smem + C::M_OFF + ms * C::M_BYTES);
 #pragma unroll
       for (int i = 0; i < C::BN / 32; ++i) {
         const int col = i * 32 + lane;
         const int n = n0 + col;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        float sk = 0.f, zk = 0.f, nks = 0.f;
         if (n < p.Skv) {
-          v.x = half_bits_to_f32(p.k_scale[tok_k0 + n]);
-          v.y = static_cast<float>(p.k_zp[tok_k0 + n]);
-          v.z = -static_cast<float>(p.k_sum[tok_k0 + n]);
+          sk = half_bits_to_f32(p.k_scale[tok_k0 + n]);
+          zk = static_cast<float>(p.k_zp[tok_k0 + n]);
+          nks = -static_cast<float>(p.k_sum[tok_k0 + n]);
         }
-        meta[col] = v;
+        meta[col] = zk;
+        meta[C::BN + col] = nks;
+        meta[2 * C::BN + col] = sk;
       }
       mbar_arrive(BAR(B_MFULL + ms));
       // V tile (D/64 panels of 128 bytes x BN rows)
@@ -245,15 +258,27 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (kwaited) mma_commit(BAR(B_KEMPTY + ks1));
       }
     }
-  } else if (warp >= 4) {
-    // ================================================================ softmax: one thread per query row
-    const int t = (warp - 4) >> 2;                 // query tile of this warpgroup
+  }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
+    // ================================================================ softmax
+    // Two threads per query row: warps sw and sw+4 of a tile share the same 32 tensor-memory lanes and
+    // take the left / right 64 columns of the S tile; they exchange the row max through shared memory.
+    const int sw = warp - 4;
+    const int t = sw >> 3;                         // query tile
+    const int half = (sw >> 2) & 1;                // column half
     const int wq = warp & 3;                       // tensor-memory lane quarter this warp may access
     const int r = wq * 32 + lane;                  // row inside the tile
     const int row = m0 + t * C::BM + r;            // global query row
+    constexpr int HC = C::BN / 2;                  // S columns per thread
+    constexpr int HD = D / 2;                      // O columns per thread
     const uint32_t lane_sel = static_cast<uint32_t>(wq * 32) << 16;
-    const uint32_t tS = tmem + lane_sel + C::S_COL + t * C::BN;
-    const uint32_t tO = tmem + lane_sel + C::O_COL + t * D;
+    const uint32_t tS = tmem + lane_sel + C::S_COL + t * C::BN + half * HC;
+    const uint32_t tP = tmem + lane_sel + C::S_COL + t * C::BN + half * (HC / 2);
+    const uint32_t tO = tmem + lane_sel + C::O_COL + t * D + half * HD;
+    const uint32_t pair_bar = BAR(B_PAIR + t * 4 + wq);
+    uint32_t pair_phase = 0;
+    float* xch = reinterpret_cast<float*>(smem + C::X_OFF);
     float A = 0.f, zq = 0.f, alpha = 0.f;
     if (row < p.Sq) {
       const int64_t tk = static_cast<int64_t>(bh) * p.Sq + row;
@@ -262,6 +287,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       A = static_cast<float>(D * z - p.q_sum[tk]);
       alpha = half_bits_to_f32(p.q_scale[tk]) * p.sm_scale * kLog2e;
     }
+    const float2 A2 = make_float2(A, A), zq2 = make_float2(zq, zq), alpha2 = make_float2(alpha, alpha);
+    const float2 negM2 = make_float2(-12582912.0f, -12582912.0f);
     float m_run = 0.f, l_run = 0.f;
     const int my_n = n_t[t];
     bool ok = true;
@@ -273,34 +300,63 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after_sync();
-        uint32_t sreg[C::BN];
+        uint32_t sreg[HC];
 #pragma unroll
-        for (int c = 0; c < C::BN / 32; ++c) tmem_ld32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sreg[c * 32]));
+        for (int c = 0; c < HC / 32; ++c) tmem_ld32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sreg[c * 32]));
         tmem_wait_ld();
-        const float4* meta = reinterpret_cast<const float4*>(smem + C::M_OFF + ms * C::M_BYTES);
-        // logits in units of 1/alpha: s_k * (S + z_k*A - sum(k)*z_q), exact up to the last multiply
-        float tmax = -INFINITY;
-        const int n0 = j * C::BN;
+        const float* meta = reinterpret_cast<const float*>(smem + C::M_OFF + ms * C::M_BYTES) + half * HC;
+        // logits in units of 1/alpha: s_k * (S + z_k*A - sum(k)*z_q); exact in fp32 up to the last multiply
+        const int n0 = j * C::BN + half * HC;
         int col_limit = p.Skv - n0;                                   // columns >= limit are masked
         if (p.causal) col_limit = min(col_limit, row + 1 - n0);
-        const bool need_mask = col_limit < C::BN;
+        const bool masked = __any_sync(0xffffffffu, col_limit < HC);
+        float tmax = -INFINITY;
 #pragma unroll
-        for (int c = 0; c < C::BN; ++c) {
-          const float4 mc = meta[c];
-          float f = static_cast<float>(static_cast<int>(sreg[c]));
-          f = fmaf(mc.y, A, f);
-          f = fmaf(mc.z, zq, f);
-          f *= mc.x;
-          if (need_mask && c >= col_limit) f = -INFINITY;
-          sreg[c] = __float_as_uint(f);
-          tmax = fmaxf(tmax, f);
+        for (int c = 0; c < HC; c += 4) {
+          const float4 y4 = *reinterpret_cast<const float4*>(meta + c);
+          const float4 z4 = *reinterpret_cast<const float4*>(meta + C::BN + c);
+          const float4 x4 = *reinterpret_cast<const float4*>(meta + 2 * C::BN + c);
+          // int32 -> fp32 without the conversion pipe: |S| <= 128*128*D < 2^22, so the bit pattern of
+          // 1.5*2^23 plus S is the float 1.5*2^23 + S
+          float2 v0 = make_float2(__uint_as_float(sreg[c] + 0x4B400000u), __uint_as_float(sreg[c + 1] + 0x4B400000u));
+          float2 v1 = make_float2(__uint_as_float(sreg[c + 2] + 0x4B400000u), __uint_as_float(sreg[c + 3] + 0x4B400000u));
+          v0 = __fadd2_rn(v0, negM2);
+          v1 = __fadd2_rn(v1, negM2);
+          v0 = __ffma2_rn(make_float2(y4.x, y4.y), A2, v0);
+          v1 = __ffma2_rn(make_float2(y4.z, y4.w), A2, v1);
+          v0 = __ffma2_rn(make_float2(z4.x, z4.y), zq2, v0);
+          v1 = __ffma2_rn(make_float2(z4.z, z4.w), zq2, v1);
+          v0 = __fmul2_rn(v0, make_float2(x4.x, x4.y));
+          v1 = __fmul2_rn(v1, make_float2(x4.z, x4.w));
+          if (masked) {
+            if (c + 0 >= col_limit) v0.x = -INFINITY;
+            if (c + 1 >= col_limit) v0.y = -INFINITY;
+            if (c + 2 >= col_limit) v1.x = -INFINITY;
+            if (c + 3 >= col_limit) v1.y = -INFINITY;
+          }
+          sreg[c] = __float_as_uint(v0.x); sreg[c + 1] = __float_as_uint(v0.y);
+          sreg[c + 2] = __float_as_uint(v1.x); sreg[c + 3] = __float_as_uint(v1.y);
+          asm("max.f32 %0, %0, %1, %2;" : "+f"(tmax) : "f"(v0.x), "f"(v0.y));
+          asm("max.f32 %0, %0, %1, %2;" : "+f"(tmax) : "f"(v1.x), "f"(v1.y));
         }
         mbar_arrive(BAR(B_MEMPTY + ms));
-        // running max with lazy rescale
+        // row max over both halves
+        {
+          float* xb = xch + ((j & 1) * C::NQT + t) * 2 * C::BM;
+          xb[half * C::BM + r] = tmax;
+          mbar_arrive(pair_bar);
+          ok = mbar_wait(pair_bar, pair_phase, abort_flag);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          pair_phase ^= 1;
+          tmax = fmaxf(tmax, xb[(half ^ 1) * C::BM + r]);
+        }
+        // running max with lazy rescale (both halves take the same decision)
         if (j == 0) {
           m_run = (tmax == -INFINITY) ? 0.f : tmax;
         } else {
           const bool grow = (tmax - m_run) * alpha > 8.0f;
+          // the partner warp sees the same rows, so the vote has the same outcome there
           if (__any_sync(0xffffffffu, grow)) {
             ok = mbar_wait(BAR(B_ODONE + t), (j - 1) & 1, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
@@ -308,32 +364,39 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             tc_fence_after_sync();
             const float m_new = fmaxf(m_run, tmax);
             const float factor = fast_exp2((m_run - m_new) * alpha);
-#pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
-              uint32_t oreg[32];
-              tmem_ld32(tO + c * 32, oreg);
+            // rare path: small chunks keep the live S row in registers
+#pragma unroll 1
+            for (int c = 0; c < HD / 8; ++c) {
+              uint32_t oreg[8];
+              tmem_ld8(tO + c * 8, oreg);
               tmem_wait_ld();
 #pragma unroll
-              for (int i = 0; i < 32; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * factor);
-              tmem_st32(tO + c * 32, oreg);
+              for (int i = 0; i < 8; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * factor);
+              tmem_st8(tO + c * 8, oreg);
             }
+            tmem_wait_st();
             l_run *= factor;
             m_run = m_new;
           }
         }
         const float neg_m = -m_run * alpha;
-        float lsum = 0.f;
-        uint32_t preg[C::BN / 2];
+        const float2 negm2 = make_float2(neg_m, neg_m);
+        float2 lsum2 = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int c = 0; c < C::BN; c += 2) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(sreg[c]), alpha, neg_m));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(sreg[c + 1]), alpha, neg_m));
-          lsum += p0 + p1;
-          preg[c / 2] = H16::pack(p0, p1);          // P rounded to 16 bit (quant_flash_attn.py:75)
+        for (int cc = 0; cc < HC; cc += 32) {
+          uint32_t preg[16];
+#pragma unroll
+          for (int c = 0; c < 32; c += 2) {
+            const float2 e = __ffma2_rn(make_float2(__uint_as_float(sreg[cc + c]), __uint_as_float(sreg[cc + c + 1])),
+                                        alpha2, negm2);
+            const float p0 = fast_exp2(e.x);
+            const float p1 = fast_exp2(e.y);
+            lsum2 = __fadd2_rn(lsum2, make_float2(p0, p1));
+            preg[c / 2] = H16::pack(p0, p1);        // P rounded to 16 bit (quant_flash_attn.py:75)
+          }
+          tmem_st16(tP + cc / 2, preg);
         }
-        l_run += lsum;
-#pragma unroll
-        for (int c = 0; c < C::BN / 64; ++c) tmem_st32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&preg[c * 32]));
+        l_run += lsum2.x + lsum2.y;
         tmem_wait_st();
         tc_fence_before_sync();
         mbar_arrive(BAR(B_PFULL + t));
@@ -347,14 +410,21 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
     // ---------------- epilogue: O / l -> 16 bit, LSE
     if (ok && my_n > 0) {
-      ok = mbar_wait(BAR(B_ODONE + t), (my_n - 1) & 1, abort_flag);
+      // total row sum = sum of the two halves' partial sums
+      float* xb = xch + t * 2 * C::BM;
+      xb[half * C::BM + r] = l_run;
+      mbar_arrive(pair_bar);
+      ok = mbar_wait(pair_bar, pair_phase, abort_flag);
+      if (ok) ok = mbar_wait(BAR(B_ODONE + t), (my_n - 1) & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (ok) {
         tc_fence_after_sync();
-        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-        T* orow = static_cast<T*>(p.o) + b * p.o_stride[0] + h * p.o_stride[1] + static_cast<int64_t>(row) * p.o_stride[2];
+        const float l_tot = l_run + xb[(half ^ 1) * C::BM + r];
+        const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
+        T* orow = static_cast<T*>(p.o) + b * p.o_stride[0] + h * p.o_stride[1] +
+                  static_cast<int64_t>(row) * p.o_stride[2] + half * HD;
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = 0; c < HD / 32; ++c) {
           uint32_t oreg[32];
           tmem_ld32(tO + c * 32, oreg);
           tmem_wait_ld();
@@ -370,8 +440,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             }
           }
         }
-        if (row < p.Sq)
-          p.lse[static_cast<int64_t>(bh) * p.lse_stride + row] = (m_run * alpha + log2f(l_run)) * kLn2;
+        if (half == 0 && row < p.Sq)
+          p.lse[static_cast<int64_t>(bh) * p.lse_stride + row] = (m_run * alpha + log2f(l_tot)) * kLn2;
       }
     }
   }
