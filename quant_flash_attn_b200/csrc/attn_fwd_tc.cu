@@ -10,16 +10,17 @@
 //
 // One CTA owns two 128-row query tiles of one (batch, head) and walks over 128-token K/V tiles.
 // Warp roles: warp 0 = TMA producer (+ per-column constants), warp 1 = MMA issuer, warp 2 = tensor
-// memory allocator, warps 4-11 / 12-19 = softmax of query tile 0 / 1: two threads per row, one per
-// 64-column half, so that four softmax warps are resident per scheduler; the halves exchange the
-// row max through shared memory, no shuffles.  The element-wise math uses packed f32x2
-// instructions.  The two query tiles ping-pong: while the softmax warps of one tile work, the
-// tensor core runs the other tile's MMAs.  O is only rescaled when the running max
-// grew by more than 2^8 (the softmax threads do it in place in tensor memory), which makes the
-// rescale rare after the first tiles.
+// memory allocator, warps 4-7 / 8-11 = softmax of query tile 0 / 1.  A softmax warp reads S in the
+// 16x256b fragment layout (a thread owns 4 rows x 32 columns), so the per-column constants are read
+// from shared memory once per four rows, row max / sum are quad shuffles, and the element-wise math
+// runs on packed f32x2 instructions in a single pass per tile: P is formed against a lazily raised
+// reference instead of the exact running max, and O, l and P are rescaled (by exact powers of two)
+// only when a tile exceeds the reference by more than 2^8.  The two query tiles ping-pong: while
+// the softmax warps of one tile work, the tensor core runs the other tile's MMAs.
 //
 // Every mbarrier wait is bounded; a wait that runs out raises a CTA-wide abort flag, all roles
 // leave their loops, tensor memory is freed and the status word is set.
+#include <atomic>
 #include <type_traits>
 
 #include "qfa_common.cuh"
@@ -39,8 +40,23 @@ struct TcFwdParams {
   int H, Sq, Skv;
   float sm_scale;
   int causal;
+  unsigned int epoch;   // distinguishes launches for the device-wide abort word
   int32_t* status;
 };
+
+// Optional timeline tracing for development builds (-DQFA_TC_TRACE): CTA 0 writes clock64() stamps of its
+// first 16 K/V steps into the buffer passed as `status` (interpreted as long long[2][16][2][8]).
+#ifdef QFA_TC_TRACE
+#define QFA_TRACE(role, j, t, idx)                                                                          \
+  do {                                                                                                      \
+    if (blockIdx.x == 0 && (j) < 16 && p.status)                                                            \
+      reinterpret_cast<long long*>(p.status)[(((role) * 16 + (j)) * 2 + (t)) * 8 + (idx)] = clock64();      \
+  } while (0)
+#else
+#define QFA_TRACE(role, j, t, idx) \
+  do {                             \
+  } while (0)
+#endif
 
 template <int D>
 struct TcCfg {
@@ -56,13 +72,11 @@ struct TcCfg {
   static constexpr int K_OFF = Q_OFF + NQT * Q_BYTES;
   static constexpr int V_OFF = K_OFF + KSTAGES * K_BYTES;
   static constexpr int M_OFF = V_OFF + VSTAGES * V_BYTES;
-  static constexpr int X_OFF = M_OFF + MSTAGES * M_BYTES;   // row-max exchange between the two column halves
-  static constexpr int X_BYTES = 2 * NQT * 2 * BM * 4;      // [parity][tile][half][row] floats
-  static constexpr int BAR_OFF = X_OFF + X_BYTES;
-  static constexpr int NBARS = 1 + 2 * KSTAGES + 2 * VSTAGES + 2 * MSTAGES + 3 * NQT + 4 * NQT;
+  static constexpr int BAR_OFF = M_OFF + MSTAGES * M_BYTES;
+  static constexpr int NBARS = 1 + 2 * KSTAGES + 2 * VSTAGES + 2 * MSTAGES + 3 * NQT;
   static constexpr int MISC_OFF = BAR_OFF + NBARS * 8;
   static constexpr int SMEM = MISC_OFF + 16 + 1024;      // + slack for 1024-byte alignment of the base
-  static constexpr int SOFTMAX_THREADS = NQT * 2 * BM;   // two threads per query row (one per column half)
+  static constexpr int SOFTMAX_THREADS = NQT * BM;       // one warp per 32 rows; a thread owns 4 rows x 32 columns
   static constexpr int THREADS = 128 + SOFTMAX_THREADS;
   // tensor memory columns
   static constexpr int S_COL = 0;                        // S_t at t*BN (int32), P_t aliases its first BN/2 columns
@@ -71,8 +85,61 @@ struct TcCfg {
   static constexpr uint32_t QK_SWIZZLE_ROWS_BYTES = 8 * D;    // 8 rows of D bytes per swizzle atom
 };
 
+// Per-row constants of a softmax thread (each thread owns four rows).  With a = s_q*sm_scale*log2(e):
+//   logit*log2e - ref = a * s_k * (S + A*z_k - z_q*sum(k)) - ref,    A = D*z_q - sum(q)
+// Every value is kept as a pair of equal halves because the math runs on packed f32x2 instructions.
+struct RowConst4 {
+  float2 a2[4], A2[4], zq2[4], nref2[4];
+};
+
+// One block of 32 columns for the four rows of a thread.  sA / sB hold the int32 accumulators of rows
+// (g, g+8) / (g+16, g+24) in the 16x256b fragment layout: element [4n + 2*(row&1) + e] is column
+// 8n + 2q + e.  `meta` points at z_k of column (block start + 2q); -sum(k) and s_k follow at +BN and +2*BN
+// floats, so the three constants of a column pair are loaded once and used for all four rows.
+// lim[k] = first masked column of row k relative to (block start + 2q).  pA / pB receive P packed to
+// 16 bit in the 16x128b store layout (word 2n + (row&1)).
+template <typename T, int BN, bool MASKED, bool MAX_ONLY>
+__device__ __forceinline__ void softmax_block(const uint32_t (&sA)[16], const uint32_t (&sB)[16], const float* meta,
+                                              const int (&lim)[4], const RowConst4& rc, float (&emax)[4],
+                                              float2 (&lsum2)[4], uint32_t* pA, uint32_t* pB) {
+  using H16 = Half16<T>;
+  const float2 negM2 = make_float2(-12582912.0f, -12582912.0f);
+#pragma unroll
+  for (int n = 0; n < 4; ++n) {
+    const float2 y2 = *reinterpret_cast<const float2*>(meta + 8 * n);
+    const float2 z2 = *reinterpret_cast<const float2*>(meta + BN + 8 * n);
+    const float2 x2 = *reinterpret_cast<const float2*>(meta + 2 * BN + 8 * n);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint32_t s0 = (k < 2) ? sA[4 * n + 2 * (k & 1)] : sB[4 * n + 2 * (k & 1)];
+      const uint32_t s1 = (k < 2) ? sA[4 * n + 2 * (k & 1) + 1] : sB[4 * n + 2 * (k & 1) + 1];
+      // int32 -> fp32 without the conversion pipe: |S| <= 128*128*D < 2^22, so the bit pattern of 1.5*2^23
+      // plus S is the float 1.5*2^23 + S.  Everything up to the multiply by s_k is exact integer arithmetic
+      // in fp32 (|S + z_k*A - sum(k)*z_q| <= 255*255*D < 2^24): with large scales one integer step is several
+      // percent of a logit, so nothing may round before that point.
+      float2 v = make_float2(__uint_as_float(s0 + 0x4B400000u), __uint_as_float(s1 + 0x4B400000u));
+      v = __fadd2_rn(v, negM2);
+      v = __ffma2_rn(y2, rc.A2[k], v);
+      v = __ffma2_rn(z2, rc.zq2[k], v);
+      v = __fmul2_rn(v, x2);
+      v = __ffma2_rn(v, rc.a2[k], rc.nref2[k]);
+      if (MASKED) {
+        if (8 * n >= lim[k]) v.x = -INFINITY;
+        if (8 * n + 1 >= lim[k]) v.y = -INFINITY;
+      }
+      asm("max.f32 %0, %0, %1, %2;" : "+f"(emax[k]) : "f"(v.x), "f"(v.y));
+      if (!MAX_ONLY) {
+        const float p0 = fast_exp2(v.x), p1 = fast_exp2(v.y);
+        lsum2[k] = __fadd2_rn(lsum2[k], make_float2(p0, p1));
+        const uint32_t w = H16::pack(p0, p1);       // P rounded to 16 bit (quant_flash_attn.py:75)
+        if (k < 2) pA[2 * n + (k & 1)] = w; else pB[2 * n + (k & 1)] = w;
+      }
+    }
+  }
+}
+
 template <typename T, int D>
-__global__ void __launch_bounds__(640, 1)
+__global__ void __launch_bounds__(384, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const TcFwdParams p) {
   using C = TcCfg<D>;
@@ -88,7 +155,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   constexpr int B_VFULL = B_KEMPTY + C::KSTAGES, B_VEMPTY = B_VFULL + C::VSTAGES;
   constexpr int B_MFULL = B_VEMPTY + C::VSTAGES, B_MEMPTY = B_MFULL + C::MSTAGES;
   constexpr int B_SFULL = B_MEMPTY + C::MSTAGES, B_PFULL = B_SFULL + C::NQT, B_ODONE = B_PFULL + C::NQT;
-  constexpr int B_PAIR = B_ODONE + C::NQT;               // [tile][lane quarter]: the two warps sharing 32 rows
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::MISC_OFF);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::MISC_OFF + 4);
 
@@ -112,16 +178,15 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   }
 
   if (tid == 0) {
-    *abort_flag = 0;
+    *abort_flag = launch_aborted(p.epoch) ? 1 : 0;     // a CTA of this launch already gave up: drain quickly
     mbar_init(BAR(B_QFULL), 1);
     for (int i = 0; i < C::KSTAGES; ++i) { mbar_init(BAR(B_KFULL + i), 1); mbar_init(BAR(B_KEMPTY + i), 1); }
     for (int i = 0; i < C::VSTAGES; ++i) { mbar_init(BAR(B_VFULL + i), 1); mbar_init(BAR(B_VEMPTY + i), 1); }
     for (int i = 0; i < C::MSTAGES; ++i) { mbar_init(BAR(B_MFULL + i), 32); mbar_init(BAR(B_MEMPTY + i), C::SOFTMAX_THREADS); }
     for (int t = 0; t < C::NQT; ++t) {
       mbar_init(BAR(B_SFULL + t), 1);
-      mbar_init(BAR(B_PFULL + t), 2 * C::BM);
+      mbar_init(BAR(B_PFULL + t), C::BM);
       mbar_init(BAR(B_ODONE + t), 1);
-      for (int w = 0; w < 4; ++w) mbar_init(BAR(B_PAIR + t * 4 + w), 64);
     }
     fence_barrier_init();
   }
@@ -137,7 +202,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   // the softmax warpgroups hold a whole 128-column row per thread: move registers to them
   if (warp < 4) {
   // control warpgroup: give registers away (the softmax warpgroups hold a whole row per thread)
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+  // Register hand-over between warpgroups.  setmaxnreg.inc BLOCKS until the CTA's pool (threads x registers
+  // the kernel was launched with) has enough free registers, so the two budgets must fit that pool or the
+  // softmax warps would wait forever.
+  static_assert(128 * 96 + C::SOFTMAX_THREADS * 192 <= C::THREADS * 168, "setmaxnreg budgets exceed the CTA's registers");
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
   if (warp == 0) {
     // ================================================================ producer
     if (lane == 0) {
@@ -154,7 +223,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const int n0 = j * C::BN;
       const int ks = j % C::KSTAGES, vs = j % C::VSTAGES, ms = j % C::MSTAGES;
       // K tile
-      ok = mbar_wait(BAR(B_KEMPTY + ks), ((j / C::KSTAGES) & 1) ^ 1, abort_flag);
+      ok = mbar_wait(BAR(B_KEMPTY + ks), ((j / C::KSTAGES) & 1) ^ 1, abort_flag, p.epoch);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       if (lane == 0) {
@@ -162,7 +231,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tma_load_4d(sbase + C::K_OFF + ks * C::K_BYTES, &tmK, BAR(B_KFULL + ks), 0, n0, h, b);
       }
       // per-column constants z_k, -sum(k), s_k
-      ok = mbar_wait(BAR(B_MEMPTY + ms), ((j / C::MSTAGES) & 1) ^ 1, abort_flag);
+      ok = mbar_wait(BAR(B_MEMPTY + ms), ((j / C::MSTAGES) & 1) ^ 1, abort_flag, p.epoch);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       float* meta = reinterpret_cast<float*>(smem + C::M_OFF + ms * C::M_BYTES);
@@ -182,7 +251,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
       mbar_arrive(BAR(B_MFULL + ms));
       // V tile (D/64 panels of 128 bytes x BN rows)
-      ok = mbar_wait(BAR(B_VEMPTY + vs), ((j / C::VSTAGES) & 1) ^ 1, abort_flag);
+      ok = mbar_wait(BAR(B_VEMPTY + vs), ((j / C::VSTAGES) & 1) ^ 1, abort_flag, p.epoch);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       if (lane == 0) {
@@ -199,7 +268,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       constexpr uint32_t kF16Fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
       constexpr uint32_t kIdescPV = make_idesc(1, kF16Fmt, kF16Fmt, 0, 1, C::BM, D);
       constexpr uint64_t kQKSwz = (D == 128) ? kSwizzle128B : kSwizzle64B;
-      bool ok = mbar_wait(BAR(B_QFULL), 0, abort_flag);
+      bool ok = mbar_wait(BAR(B_QFULL), 0, abort_flag, p.epoch);
       tc_fence_after_sync();
 
       auto issue_qk = [&](int j, int t) {
@@ -222,7 +291,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       };
 
       if (ok && n_max > 0) {
-        ok = mbar_wait(BAR(B_KFULL + 0), 0, abort_flag);
+        ok = mbar_wait(BAR(B_KFULL + 0), 0, abort_flag, p.epoch);
         if (ok) {
           tc_fence_after_sync();
           for (int t = 0; t < C::NQT; ++t)
@@ -232,25 +301,29 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
       for (int j = 0; j < n_max && ok; ++j) {
         const int vs = j % C::VSTAGES;
-        ok = mbar_wait(BAR(B_VFULL + vs), (j / C::VSTAGES) & 1, abort_flag);
+        ok = mbar_wait(BAR(B_VFULL + vs), (j / C::VSTAGES) & 1, abort_flag, p.epoch);
         if (!ok) break;
         const int ks1 = (j + 1) % C::KSTAGES;
         bool kwaited = false;
         for (int t = 0; t < C::NQT && ok; ++t) {
           if (j < n_t[t]) {
-            ok = mbar_wait(BAR(B_PFULL + t), j & 1, abort_flag);
+            QFA_TRACE(1, j, t, 0);
+            ok = mbar_wait(BAR(B_PFULL + t), j & 1, abort_flag, p.epoch);
             if (!ok) break;
             tc_fence_after_sync();
+            QFA_TRACE(1, j, t, 1);
             issue_pv(j, t);
+            QFA_TRACE(1, j, t, 2);
           }
           if (j + 1 < n_t[t]) {
             if (!kwaited) {
-              ok = mbar_wait(BAR(B_KFULL + ks1), ((j + 1) / C::KSTAGES) & 1, abort_flag);
+              ok = mbar_wait(BAR(B_KFULL + ks1), ((j + 1) / C::KSTAGES) & 1, abort_flag, p.epoch);
               if (!ok) break;
               tc_fence_after_sync();
               kwaited = true;
             }
             issue_qk(j + 1, t);
+            QFA_TRACE(1, j, t, 3);
           }
         }
         if (!ok) break;
@@ -260,171 +333,220 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
   }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 192;");
     // ================================================================ softmax
-    // Two threads per query row: warps sw and sw+4 of a tile share the same 32 tensor-memory lanes and
-    // take the left / right 64 columns of the S tile; they exchange the row max through shared memory.
-    const int sw = warp - 4;
-    const int t = sw >> 3;                         // query tile
-    const int half = (sw >> 2) & 1;                // column half
+    // One warp per 32 rows of a query tile.  S is read in the 16x256b fragment layout: thread (g, q) of the
+    // warp owns rows g, g+8, g+16, g+24 of its lane quarter and columns 8n+2q, 8n+2q+1, so the three
+    // per-column constants are fetched from shared memory once per four rows and row reductions are
+    // two quad shuffles.  P = exp2(logit - ref) is formed in the same pass that finds the tile max, against a
+    // reference that is only raised (by a whole number: exact power-of-two rescale of O, l and P) when a
+    // tile exceeds it by more than 2^8; after the first tiles that almost never happens.
+    const int t = (warp - 4) >> 2;                 // query tile of this warpgroup
     const int wq = warp & 3;                       // tensor-memory lane quarter this warp may access
-    const int r = wq * 32 + lane;                  // row inside the tile
-    const int row = m0 + t * C::BM + r;            // global query row
-    constexpr int HC = C::BN / 2;                  // S columns per thread
-    constexpr int HD = D / 2;                      // O columns per thread
-    const uint32_t lane_sel = static_cast<uint32_t>(wq * 32) << 16;
-    const uint32_t tS = tmem + lane_sel + C::S_COL + t * C::BN + half * HC;
-    const uint32_t tP = tmem + lane_sel + C::S_COL + t * C::BN + half * (HC / 2);
-    const uint32_t tO = tmem + lane_sel + C::O_COL + t * D + half * HD;
-    const uint32_t pair_bar = BAR(B_PAIR + t * 4 + wq);
-    uint32_t pair_phase = 0;
-    float* xch = reinterpret_cast<float*>(smem + C::X_OFF);
-    float A = 0.f, zq = 0.f, alpha = 0.f;
-    if (row < p.Sq) {
-      const int64_t tk = static_cast<int64_t>(bh) * p.Sq + row;
-      const int z = p.q_zp[tk];
-      zq = static_cast<float>(z);
-      A = static_cast<float>(D * z - p.q_sum[tk]);
-      alpha = half_bits_to_f32(p.q_scale[tk]) * p.sm_scale * kLog2e;
+    const int g = lane >> 2, q = lane & 3;
+    const uint32_t quarter = static_cast<uint32_t>(wq * 32) << 16;
+    const uint32_t tS = tmem + quarter + C::S_COL + t * C::BN;
+    const uint32_t tO = tmem + quarter + C::O_COL + t * D;
+    constexpr uint32_t kLane16 = 16u << 16;
+    int rowk[4];
+    RowConst4 rc;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      rowk[k] = m0 + t * C::BM + wq * 32 + g + 8 * k;
+      float A = 0.f, zq = 0.f, a = 0.f;
+      if (rowk[k] < p.Sq) {
+        const int64_t tk = static_cast<int64_t>(bh) * p.Sq + rowk[k];
+        const int z = p.q_zp[tk];
+        zq = static_cast<float>(z);
+        A = static_cast<float>(D * z - p.q_sum[tk]);
+        a = half_bits_to_f32(p.q_scale[tk]) * p.sm_scale * kLog2e;
+      }
+      rc.a2[k] = make_float2(a, a);
+      rc.A2[k] = make_float2(A, A);
+      rc.zq2[k] = make_float2(zq, zq);
+      rc.nref2[k] = make_float2(0.f, 0.f);
     }
-    const float2 A2 = make_float2(A, A), zq2 = make_float2(zq, zq), alpha2 = make_float2(alpha, alpha);
-    const float2 negM2 = make_float2(-12582912.0f, -12582912.0f);
-    float m_run = 0.f, l_run = 0.f;
+    // largest excess over the reference that may be fixed by rescaling P in registers (P must not have
+    // overflowed its 16-bit type); beyond that the tile is recomputed from S, which is still intact
+    constexpr float kInRegMax = std::is_same<T, __half>::value ? 15.0f : 100.0f;
+    float ref[4] = {0.f, 0.f, 0.f, 0.f}, l_run[4] = {0.f, 0.f, 0.f, 0.f};
     const int my_n = n_t[t];
     bool ok = true;
     for (int j = 0; j < n_max && ok; ++j) {
       const int ms = j % C::MSTAGES;
       if (j < my_n) {
-        ok = mbar_wait(BAR(B_MFULL + ms), (j / C::MSTAGES) & 1, abort_flag);
-        if (ok) ok = mbar_wait(BAR(B_SFULL + t), j & 1, abort_flag);
+        const bool tr = (wq == 0 && lane == 0);
+        if (tr) QFA_TRACE(0, j, t, 0);
+        ok = mbar_wait(BAR(B_MFULL + ms), (j / C::MSTAGES) & 1, abort_flag, p.epoch);
+        if (ok) ok = mbar_wait(BAR(B_SFULL + t), j & 1, abort_flag, p.epoch);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after_sync();
-        uint32_t sreg[HC];
+        if (tr) QFA_TRACE(0, j, t, 1);
+        const float* meta = reinterpret_cast<const float*>(smem + C::M_OFF + ms * C::M_BYTES) + 2 * q;
+        const int n0 = j * C::BN;
+        int lim[4];                                   // first masked column of each row, relative to 2q
+        bool any_masked = false;
 #pragma unroll
-        for (int c = 0; c < HC / 32; ++c) tmem_ld32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sreg[c * 32]));
-        tmem_wait_ld();
-        const float* meta = reinterpret_cast<const float*>(smem + C::M_OFF + ms * C::M_BYTES) + half * HC;
-        // logits in units of 1/alpha: s_k * (S + z_k*A - sum(k)*z_q); exact in fp32 up to the last multiply
-        const int n0 = j * C::BN + half * HC;
-        int col_limit = p.Skv - n0;                                   // columns >= limit are masked
-        if (p.causal) col_limit = min(col_limit, row + 1 - n0);
-        const bool masked = __any_sync(0xffffffffu, col_limit < HC);
-        float tmax = -INFINITY;
+        for (int k = 0; k < 4; ++k) {
+          int cl = p.Skv - n0;
+          if (p.causal) cl = min(cl, rowk[k] + 1 - n0);
+          any_masked |= cl < C::BN;
+          lim[k] = cl - 2 * q;
+        }
+        const bool masked = __any_sync(0xffffffffu, any_masked);
+        float emax[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        float2 lsum2[4];
 #pragma unroll
-        for (int c = 0; c < HC; c += 4) {
-          const float4 y4 = *reinterpret_cast<const float4*>(meta + c);
-          const float4 z4 = *reinterpret_cast<const float4*>(meta + C::BN + c);
-          const float4 x4 = *reinterpret_cast<const float4*>(meta + 2 * C::BN + c);
-          // int32 -> fp32 without the conversion pipe: |S| <= 128*128*D < 2^22, so the bit pattern of
-          // 1.5*2^23 plus S is the float 1.5*2^23 + S
-          float2 v0 = make_float2(__uint_as_float(sreg[c] + 0x4B400000u), __uint_as_float(sreg[c + 1] + 0x4B400000u));
-          float2 v1 = make_float2(__uint_as_float(sreg[c + 2] + 0x4B400000u), __uint_as_float(sreg[c + 3] + 0x4B400000u));
-          v0 = __fadd2_rn(v0, negM2);
-          v1 = __fadd2_rn(v1, negM2);
-          v0 = __ffma2_rn(make_float2(y4.x, y4.y), A2, v0);
-          v1 = __ffma2_rn(make_float2(y4.z, y4.w), A2, v1);
-          v0 = __ffma2_rn(make_float2(z4.x, z4.y), zq2, v0);
-          v1 = __ffma2_rn(make_float2(z4.z, z4.w), zq2, v1);
-          v0 = __fmul2_rn(v0, make_float2(x4.x, x4.y));
-          v1 = __fmul2_rn(v1, make_float2(x4.z, x4.w));
-          if (masked) {
-            if (c + 0 >= col_limit) v0.x = -INFINITY;
-            if (c + 1 >= col_limit) v0.y = -INFINITY;
-            if (c + 2 >= col_limit) v1.x = -INFINITY;
-            if (c + 3 >= col_limit) v1.y = -INFINITY;
+        for (int k = 0; k < 4; ++k) lsum2[k] = make_float2(0.f, 0.f);
+        uint32_t pA[32], pB[32];                      // P of rows (g, g+8) / (g+16, g+24), 64 packed columns
+        uint32_t sA[16], sB[16];
+
+        // processes the whole tile; MAXONLY computes only the row maxima (first tile)
+        auto run_tile = [&](auto maxonly_tag, auto masked_tag) {
+          constexpr bool MAXONLY = decltype(maxonly_tag)::value;
+          constexpr bool MASKED = decltype(masked_tag)::value;
+#pragma unroll
+          for (int blk = 0; blk < C::BN / 32; ++blk) {
+            tmem_ld_16x256b_x4(tS + blk * 32, sA);
+            tmem_ld_16x256b_x4(tS + kLane16 + blk * 32, sB);
+            tmem_wait_ld();
+            int lim_b[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) lim_b[k] = lim[k] - blk * 32;
+            softmax_block<T, C::BN, MASKED, MAXONLY>(sA, sB, meta + blk * 32, lim_b, rc, emax, lsum2, pA + blk * 8,
+                                                     pB + blk * 8);
           }
-          sreg[c] = __float_as_uint(v0.x); sreg[c + 1] = __float_as_uint(v0.y);
-          sreg[c + 2] = __float_as_uint(v1.x); sreg[c + 3] = __float_as_uint(v1.y);
-          asm("max.f32 %0, %0, %1, %2;" : "+f"(tmax) : "f"(v0.x), "f"(v0.y));
-          asm("max.f32 %0, %0, %1, %2;" : "+f"(tmax) : "f"(v1.x), "f"(v1.y));
-        }
-        mbar_arrive(BAR(B_MEMPTY + ms));
-        // row max over both halves
-        {
-          float* xb = xch + ((j & 1) * C::NQT + t) * 2 * C::BM;
-          xb[half * C::BM + r] = tmax;
-          mbar_arrive(pair_bar);
-          ok = mbar_wait(pair_bar, pair_phase, abort_flag);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          pair_phase ^= 1;
-          tmax = fmaxf(tmax, xb[(half ^ 1) * C::BM + r]);
-        }
-        // running max with lazy rescale (both halves take the same decision)
+        };
+        auto quad_max = [&]() {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            emax[k] = fmaxf(emax[k], __shfl_xor_sync(0xffffffffu, emax[k], 1));
+            emax[k] = fmaxf(emax[k], __shfl_xor_sync(0xffffffffu, emax[k], 2));
+          }
+        };
+
         if (j == 0) {
-          m_run = (tmax == -INFINITY) ? 0.f : tmax;
-        } else {
-          const bool grow = (tmax - m_run) * alpha > 8.0f;
-          // the partner warp sees the same rows, so the vote has the same outcome there
-          if (__any_sync(0xffffffffu, grow)) {
-            ok = mbar_wait(BAR(B_ODONE + t), (j - 1) & 1, abort_flag);
+          // no reference yet: take the exact row max of the first tile
+          if (masked) run_tile(std::true_type{}, std::true_type{}); else run_tile(std::true_type{}, std::false_type{});
+          quad_max();
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            ref[k] = (emax[k] == -INFINITY) ? 0.f : emax[k];
+            rc.nref2[k] = make_float2(-ref[k], -ref[k]);
+            emax[k] = -INFINITY;
+          }
+        }
+        if (masked) run_tile(std::false_type{}, std::true_type{}); else run_tile(std::false_type{}, std::false_type{});
+        if (tr) QFA_TRACE(0, j, t, 3);
+        quad_max();
+
+        // ---- rare: some row exceeded its reference by more than 2^8
+        bool grow = false;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) grow |= emax[k] > 8.0f;
+        if (__any_sync(0xffffffffu, grow)) {
+          float kf[4], factor[4];
+          bool redo = false;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            kf[k] = (emax[k] > 8.0f) ? ceilf(emax[k]) : 0.f;       // whole number: 2^-kf is exact
+            factor[k] = fast_exp2(-kf[k]);
+            redo |= emax[k] > kInRegMax;
+          }
+          if (j > 0) {
+            ok = mbar_wait(BAR(B_ODONE + t), (j - 1) & 1, abort_flag, p.epoch);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after_sync();
-            const float m_new = fmaxf(m_run, tmax);
-            const float factor = fast_exp2((m_run - m_new) * alpha);
-            // rare path: small chunks keep the live S row in registers
+            // O is rescaled in the plain row-per-thread layout: fetch the factor of row `lane`
+            float f_row = 1.f;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const float f = __shfl_sync(0xffffffffu, factor[k], 4 * (lane & 7));
+              if ((lane >> 3) == k) f_row = f;
+            }
 #pragma unroll 1
-            for (int c = 0; c < HD / 8; ++c) {
+            for (int c = 0; c < D / 8; ++c) {
               uint32_t oreg[8];
               tmem_ld8(tO + c * 8, oreg);
               tmem_wait_ld();
 #pragma unroll
-              for (int i = 0; i < 8; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * factor);
+              for (int i = 0; i < 8; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * f_row);
               tmem_st8(tO + c * 8, oreg);
             }
             tmem_wait_st();
-            l_run *= factor;
-            m_run = m_new;
+          }
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            l_run[k] *= factor[k];
+            ref[k] += kf[k];
+            rc.nref2[k] = make_float2(-ref[k], -ref[k]);
+          }
+          if (__any_sync(0xffffffffu, redo)) {
+            // P may have overflowed its 16-bit type: recompute the tile against the new reference
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { lsum2[k] = make_float2(0.f, 0.f); emax[k] = -INFINITY; }
+            run_tile(std::false_type{}, std::true_type{});
+          } else {
+            // exact power-of-two rescale of the P already packed in registers and of its row sums
+            uint32_t f2[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { f2[k] = H16::pack(factor[k], factor[k]); lsum2[k].x *= factor[k]; lsum2[k].y *= factor[k]; }
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              typename H16::T2 va = __hmul2(*reinterpret_cast<typename H16::T2*>(&pA[i]),
+                                            *reinterpret_cast<const typename H16::T2*>(&f2[i & 1]));
+              typename H16::T2 vb = __hmul2(*reinterpret_cast<typename H16::T2*>(&pB[i]),
+                                            *reinterpret_cast<const typename H16::T2*>(&f2[2 + (i & 1)]));
+              pA[i] = *reinterpret_cast<uint32_t*>(&va);
+              pB[i] = *reinterpret_cast<uint32_t*>(&vb);
+            }
           }
         }
-        const float neg_m = -m_run * alpha;
-        const float2 negm2 = make_float2(neg_m, neg_m);
-        float2 lsum2 = make_float2(0.f, 0.f);
+        mbar_arrive(BAR(B_MEMPTY + ms));
 #pragma unroll
-        for (int cc = 0; cc < HC; cc += 32) {
-          uint32_t preg[16];
-#pragma unroll
-          for (int c = 0; c < 32; c += 2) {
-            const float2 e = __ffma2_rn(make_float2(__uint_as_float(sreg[cc + c]), __uint_as_float(sreg[cc + c + 1])),
-                                        alpha2, negm2);
-            const float p0 = fast_exp2(e.x);
-            const float p1 = fast_exp2(e.y);
-            lsum2 = __fadd2_rn(lsum2, make_float2(p0, p1));
-            preg[c / 2] = H16::pack(p0, p1);        // P rounded to 16 bit (quant_flash_attn.py:75)
-          }
-          tmem_st16(tP + cc / 2, preg);
-        }
-        l_run += lsum2.x + lsum2.y;
+        for (int k = 0; k < 4; ++k) l_run[k] += lsum2[k].x + lsum2[k].y;
+        if (tr) QFA_TRACE(0, j, t, 5);
+        tmem_st_16x128b_x16(tS, pA);
+        tmem_st_16x128b_x16(tS + kLane16, pB);
+        if (tr) QFA_TRACE(0, j, t, 6);
         tmem_wait_st();
         tc_fence_before_sync();
         mbar_arrive(BAR(B_PFULL + t));
+        if (tr) QFA_TRACE(0, j, t, 7);
       } else {
         // this query tile is done (causal): keep the per-column ring moving for the other tile
-        ok = mbar_wait(BAR(B_MFULL + ms), (j / C::MSTAGES) & 1, abort_flag);
+        ok = mbar_wait(BAR(B_MFULL + ms), (j / C::MSTAGES) & 1, abort_flag, p.epoch);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         mbar_arrive(BAR(B_MEMPTY + ms));
       }
     }
-    // ---------------- epilogue: O / l -> 16 bit, LSE
+    // ---------------- epilogue: O / l -> 16 bit, LSE = (ref + log2 l) ln 2
     if (ok && my_n > 0) {
-      // total row sum = sum of the two halves' partial sums
-      float* xb = xch + t * 2 * C::BM;
-      xb[half * C::BM + r] = l_run;
-      mbar_arrive(pair_bar);
-      ok = mbar_wait(pair_bar, pair_phase, abort_flag);
-      if (ok) ok = mbar_wait(BAR(B_ODONE + t), (my_n - 1) & 1, abort_flag);
+      ok = mbar_wait(BAR(B_ODONE + t), (my_n - 1) & 1, abort_flag, p.epoch);
       ok = __all_sync(0xffffffffu, ok);
       if (ok) {
         tc_fence_after_sync();
-        const float l_tot = l_run + xb[(half ^ 1) * C::BM + r];
-        const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
-        T* orow = static_cast<T*>(p.o) + b * p.o_stride[0] + h * p.o_stride[1] +
-                  static_cast<int64_t>(row) * p.o_stride[2] + half * HD;
+        // row sums: the four threads of a quad hold partial sums of the same rows
+        float inv_row = 0.f;
 #pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {
+        for (int k = 0; k < 4; ++k) {
+          float l = l_run[k];
+          l += __shfl_xor_sync(0xffffffffu, l, 1);
+          l += __shfl_xor_sync(0xffffffffu, l, 2);
+          if (q == 0 && rowk[k] < p.Sq)
+            p.lse[static_cast<int64_t>(bh) * p.lse_stride + rowk[k]] = (ref[k] + log2f(l)) * kLn2;
+          const float inv = l > 0.f ? 1.f / l : 0.f;
+          // O is read in the plain row-per-thread layout: hand row `lane` its 1/l
+          const float v = __shfl_sync(0xffffffffu, inv, 4 * (lane & 7));
+          if ((lane >> 3) == k) inv_row = v;
+        }
+        const int row = m0 + t * C::BM + wq * 32 + lane;
+        T* orow = static_cast<T*>(p.o) + b * p.o_stride[0] + h * p.o_stride[1] + static_cast<int64_t>(row) * p.o_stride[2];
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
           uint32_t oreg[32];
           tmem_ld32(tO + c * 32, oreg);
           tmem_wait_ld();
@@ -432,16 +554,14 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {
               uint4 v;
-              v.x = H16::pack(__uint_as_float(oreg[i]) * inv, __uint_as_float(oreg[i + 1]) * inv);
-              v.y = H16::pack(__uint_as_float(oreg[i + 2]) * inv, __uint_as_float(oreg[i + 3]) * inv);
-              v.z = H16::pack(__uint_as_float(oreg[i + 4]) * inv, __uint_as_float(oreg[i + 5]) * inv);
-              v.w = H16::pack(__uint_as_float(oreg[i + 6]) * inv, __uint_as_float(oreg[i + 7]) * inv);
+              v.x = H16::pack(__uint_as_float(oreg[i]) * inv_row, __uint_as_float(oreg[i + 1]) * inv_row);
+              v.y = H16::pack(__uint_as_float(oreg[i + 2]) * inv_row, __uint_as_float(oreg[i + 3]) * inv_row);
+              v.z = H16::pack(__uint_as_float(oreg[i + 4]) * inv_row, __uint_as_float(oreg[i + 5]) * inv_row);
+              v.w = H16::pack(__uint_as_float(oreg[i + 6]) * inv_row, __uint_as_float(oreg[i + 7]) * inv_row);
               *reinterpret_cast<uint4*>(orow + c * 32 + i) = v;
             }
           }
         }
-        if (half == 0 && row < p.Sq)
-          p.lse[static_cast<int64_t>(bh) * p.lse_stride + row] = (m_run * alpha + log2f(l_tot)) * kLn2;
       }
     }
   }
@@ -453,7 +573,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     tc_fence_after_sync();
     tmem_dealloc(tmem, C::TMEM_COLS);
   }
+#ifndef QFA_TC_TRACE
   if (tid == 0 && *abort_flag && p.status) *p.status = QFA_STATUS_WAIT_TIMEOUT;
+#endif
 }
 
 template <typename T, int D>
@@ -478,6 +600,9 @@ static int launch_tc(const QfaFwdArgs& a, cudaStream_t stream) {
   p.lse = a.lse; p.lse_stride = a.lse_stride;
   p.H = static_cast<int>(a.H); p.Sq = static_cast<int>(a.Sq); p.Skv = static_cast<int>(a.Skv);
   p.sm_scale = a.sm_scale; p.causal = a.causal; p.status = a.status;
+  static std::atomic<unsigned int> epoch_counter{0};
+  p.epoch = epoch_counter.fetch_add(1, std::memory_order_relaxed) + 1;
+  if (p.epoch == 0) p.epoch = epoch_counter.fetch_add(1, std::memory_order_relaxed) + 1;
   auto kern = attn_fwd_tc_kernel<T, D>;
   static bool attr_done[64] = {};
   int devid = 0;

@@ -38,16 +38,35 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uin
   return ok != 0;
 }
 
-// Bounded wait.  Returns false when the wait was abandoned: either this thread ran out of tries
-// (it then raises *abort_flag, a shared-memory word), or another thread of the CTA already did.
-// Callers leave their role loop on false; nobody spins forever and nothing traps.
-constexpr uint32_t kWaitTries = 1u << 22;
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t it = 0; it < kWaitTries; ++it) {
+// Bounded wait.  Returns false when the wait was abandoned: this thread waited longer than kWaitBudgetNs
+// (it then raises *abort_flag, a shared-memory word, and the device-wide g_abort_epoch), or another thread
+// of the CTA / another CTA of the same launch already did.  Callers leave their role loop on false; nobody
+// spins forever and nothing traps.  A healthy wait lasts microseconds, so the budget only matters for a
+// protocol bug, and then the whole launch drains within a fraction of a second.
+constexpr unsigned long long kWaitBudgetNs = 200ull * 1000 * 1000;
+__device__ unsigned int g_abort_epoch = 0;     // launch epoch in which a wait ran out (0 = never)
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ bool launch_aborted(unsigned int epoch) {
+  return *reinterpret_cast<volatile unsigned int*>(&g_abort_epoch) == epoch;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          unsigned int epoch) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+  for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 63u) == 63u && *abort_flag) return false;
+    if ((it & 15u) == 0u) {
+      if (*abort_flag || launch_aborted(epoch)) return false;
+      if (global_timer_ns() - t0 > kWaitBudgetNs) break;
+    }
   }
   *abort_flag = 1;
+  *reinterpret_cast<volatile unsigned int*>(&g_abort_epoch) = epoch;
   return false;
 }
 
@@ -110,6 +129,32 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+// 16 lanes x 256 bit, 4 repetitions (32 columns): thread (g = t/4, q = t%4) gets, for repetition n,
+// r[4n+0..1] = lane g, columns 8n+2q, 8n+2q+1 and r[4n+2..3] = lane g+8, same columns (the layout of
+// an mma.sync accumulator fragment).  The lane field of the address selects lanes 0-15 or 16-31 of
+// the warp's 32-lane quarter.
+__device__ __forceinline__ void tmem_ld_16x256b_x4(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x4.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+// 16 lanes x 128 bit, 16 repetitions (64 columns): thread (g, q) supplies, for repetition n,
+// r[2n] -> lane g, column 4n+q and r[2n+1] -> lane g+8, column 4n+q.
+__device__ __forceinline__ void tmem_st_16x128b_x16(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.16x128b.x16.b32 [%0], "
       "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
       "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
       ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),

@@ -15,6 +15,7 @@ handed to the library as raw pointers.
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import torch
 
@@ -146,15 +147,23 @@ def int8_attention_forward(qq, kq, vq, causal: bool, sm_scale: float, dtype: tor
         o = torch.empty((B, H, Sq, D), dtype=dtype, device=qc.device)
     if lse is None:
         lse = torch.empty((B, H, Sq), dtype=torch.float32, device=qc.device)
+    # QFA_CHECK_STATUS=1 (debugging aid): give the kernel a status word, synchronise and raise if a bounded
+    # wait inside the kernel ran out
+    status = torch.zeros(1, dtype=torch.int32, device=qc.device) if os.environ.get("QFA_CHECK_STATUS") else None
     args = _lib.QfaFwdArgs(
         mode=_lib.QFA_MODE_INT8, dtype=_DT[dtype], causal=int(bool(causal)), sm_scale=float(sm_scale),
         B=B, H=H, Sq=Sq, Skv=Skv, D=D, q=None, q_stride=_lib.c_i64x3(0, 0, 0),
         qq=_quant_tensor(qc, qs, qz, qsum), k=_quant_tensor(kc, ks, kz, ksum), v=_quant_tensor(vc, vs, vz),
         v_hat=vhat.data_ptr() if vhat is not None else None,
-        o=o.data_ptr(), o_stride=_s3(o), lse=lse.data_ptr(), lse_stride=Sq, status=None)
+        o=o.data_ptr(), o_stride=_s3(o), lse=lse.data_ptr(), lse_stride=Sq,
+        status=status.data_ptr() if status is not None else None)
     with torch.cuda.device(qc.device):
         rc = _lib.load().qfa_attn_fwd(C.byref(args), _stream(qc))
     _lib.check(rc, "qfa_attn_fwd")
+    if status is not None:
+        code = int(status.item())
+        if code:
+            raise RuntimeError(f"qfa_attn_fwd kernel status {code}: {_lib.load().qfa_strerror(code).decode()}")
     return o, lse
 
 
