@@ -24,6 +24,10 @@ int attn_fwd_mma_entry(const QfaFwdArgs& a, cudaStream_t stream);
 int attn_fwd_tc_supported(const QfaFwdArgs& a);
 int attn_fwd_tc_entry(const QfaFwdArgs& a, cudaStream_t stream);
 int attn_bwd_mma_entry(const QfaBwdArgs& a, float* dq_accum, cudaStream_t stream);
+int attn_fwd_shortq_supported(const QfaFwdArgs& a);
+int attn_fwd_shortq_entry(const QfaFwdArgs& a, cudaStream_t stream);
+int attn_bwd_shortq_supported(const QfaBwdArgs& a);
+int attn_bwd_shortq_entry(const QfaBwdArgs& a, cudaStream_t stream);
 int attn_bwd_delta_entry(const void* o, const int64_t* so, const void* d_o, const int64_t* sd, float* delta,
                          int64_t delta_stride, int64_t B, int64_t H, int64_t Sq, int64_t D, int dtype,
                          cudaStream_t stream);
@@ -84,6 +88,7 @@ QFA_API int qfa_attn_fwd(const QfaFwdArgs* a, qfa_stream_t stream) {
   if ((rc = check_quant_tensor(a->v, false))) return rc;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (attn_fwd_tc_supported(*a)) return attn_fwd_tc_entry(*a, s);
+  if (attn_fwd_shortq_supported(*a)) return attn_fwd_shortq_entry(*a, s);
   return attn_fwd_mma_entry(*a, s);
 }
 
@@ -121,6 +126,7 @@ QFA_API int qfa_attn_bwd(const QfaBwdArgs* a, qfa_stream_t stream) {
   if ((rc = check_quant_tensor(a->k, a->mode == QFA_MODE_INT8))) return rc;
   if ((rc = check_quant_tensor(a->v, false))) return rc;
   if (a->dkv_fused && (a->k.codes != a->v.codes || a->k.scale != a->v.scale || a->k.zp != a->v.zp)) return QFA_ERR_MODE;
+  if (attn_bwd_shortq_supported(*a)) return attn_bwd_shortq_entry(*a, reinterpret_cast<cudaStream_t>(stream));
   return attn_bwd_mma_entry(*a, a->dq_accum, reinterpret_cast<cudaStream_t>(stream));
 }
 
