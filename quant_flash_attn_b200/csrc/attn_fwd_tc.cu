@@ -622,7 +622,7 @@ static int launch_tc(const QfaFwdArgs& a, cudaStream_t stream) {
 // The tcgen05 kernel takes int8-mode problems with the dequantized V supplied by the quantizer.
 int attn_fwd_tc_supported(const QfaFwdArgs& a) {
   if (a.mode != QFA_MODE_INT8 || !a.v_hat) return 0;
-  if (a.D != 128) return 0;
+  if (a.D != 128 && a.D != 64) return 0;
   if (!(a.sm_scale > 0.f)) return 0;
   if ((reinterpret_cast<uintptr_t>(a.v_hat) & 15) != 0) return 0;
   return 1;
@@ -631,6 +631,9 @@ int attn_fwd_tc_supported(const QfaFwdArgs& a) {
 int attn_fwd_tc_entry(const QfaFwdArgs& a, cudaStream_t stream) {
   if (a.D == 128) {
     return a.dtype == QFA_BF16 ? launch_tc<__nv_bfloat16, 128>(a, stream) : launch_tc<__half, 128>(a, stream);
+  }
+  if (a.D == 64) {
+    return a.dtype == QFA_BF16 ? launch_tc<__nv_bfloat16, 64>(a, stream) : launch_tc<__half, 64>(a, stream);
   }
   return QFA_ERR_HEAD_DIM;
 }
