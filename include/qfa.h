@@ -77,6 +77,13 @@ QFA_API int qfa_quant_dequant_per_token(const void* x, int8_t* codes, uint16_t* 
                                 int64_t sx_z, int64_t sx_h, int64_t sx_m, int64_t sx_k,
                                 int dtype, qfa_stream_t stream);
 
+/* Dequantize: out[token][:] = (code - zp) * fp16(scale) rounded to `dtype`, the operand the reference
+ * builds at quant_flash_attn.py:65-66 / :150-151.  codes (Z,H,M,D) with element strides s_z, s_h, s_m (inner
+ * stride 1, D a multiple of 16); scale / zp contiguous over tokens; out contiguous (Z,H,M,D). */
+QFA_API int qfa_dequant_per_token(const int8_t* codes, const uint16_t* scale_f16, const int8_t* zp, void* out,
+                                  int64_t Z, int64_t H, int64_t M, int64_t D,
+                                  int64_t s_z, int64_t s_h, int64_t s_m, int dtype, qfa_stream_t stream);
+
 /* ---------------------------------------------------------------------------------------------
  * One quantized operand of the attention kernels: codes (B,H,S,D) with element strides (inner
  * stride 1), and per-token scale / zero-point / code-sum arrays contiguous over (B*H*S).
@@ -129,8 +136,9 @@ QFA_API int qfa_attn_bwd_delta(const void* o, const int64_t o_stride[3], const v
  *   dq            16-bit (B,H,Sq,D)
  *   dk, dv        16-bit (B,H,Skv,D).  If `dkv_fused` is non-zero only `dk` is written and holds
  *                 dV + sm_scale*dK as the reference does (quant_flash_attn.py:161); requires k == v.
- * dq_accum: fp32 scratch, contiguous (B,H,Sq,D), owned by the caller; the kernel zero-fills it,
- * accumulates dQ into it with atomics and converts it into dq.
+ * dq_accum: fp32 scratch, contiguous (B,H,Sq,D), owned by the caller; the mma.sync kernel zero-fills it,
+ * accumulates dQ into it with atomics and converts it into dq (the short-query and tcgen05 kernels do not
+ * touch it).
  * Gradients: dq = sm_scale * dS.K^, dk = sm_scale * dS^T.Q, dv = P^T.dO.
  */
 typedef struct {
@@ -153,6 +161,12 @@ typedef struct {
   int64_t dv_stride[3];
   float* dq_accum;
   int32_t* status;
+  /* Optional (QFA_MODE_INT8): dequantized Q, K, V as 16-bit contiguous (B,H,S,D) tensors
+   * (qfa_dequant_per_token / qfa_quant_dequant_per_token).  When all three are given and the head
+   * dimension is 64 or 128 the tcgen05 backward kernels run and dq_accum is not used. */
+  const void* q_hat;
+  const void* k_hat;
+  const void* v_hat;
 } QfaBwdArgs;
 
 QFA_API int qfa_attn_bwd(const QfaBwdArgs* args, qfa_stream_t stream);

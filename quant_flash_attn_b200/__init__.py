@@ -13,7 +13,7 @@ from .asymmetric_quant import (  # noqa: F401
 )
 from .quant_flash_attn import (  # noqa: F401
     QuantFlashAttention, quant_flash_attn, QuantAttention, quant_attention,
-    quantize_qkv, int8_attention_forward, int8_attention_backward,
+    quantize_qkv, int8_attention_forward, int8_attention_backward, dequantize_16bit,
 )
 from .sharding import head_slice, shard_bounds  # noqa: F401
 from ._lib import launch_count  # noqa: F401
@@ -21,6 +21,6 @@ from ._lib import launch_count  # noqa: F401
 __all__ = [
     "asymmetric_quant_per_token", "asymmetric_quant_per_token_ex", "dequantize_per_token",
     "QuantFlashAttention", "quant_flash_attn", "QuantAttention", "quant_attention",
-    "quantize_qkv", "int8_attention_forward", "int8_attention_backward",
+    "quantize_qkv", "int8_attention_forward", "int8_attention_backward", "dequantize_16bit",
     "head_slice", "shard_bounds", "launch_count",
 ]

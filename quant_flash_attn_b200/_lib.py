@@ -43,7 +43,8 @@ class QfaBwdArgs(C.Structure):
                 ("dq", C.c_void_p), ("dq_stride", c_i64x3),
                 ("dk", C.c_void_p), ("dk_stride", c_i64x3),
                 ("dv", C.c_void_p), ("dv_stride", c_i64x3),
-                ("dq_accum", C.c_void_p), ("status", C.c_void_p)]
+                ("dq_accum", C.c_void_p), ("status", C.c_void_p),
+                ("q_hat", C.c_void_p), ("k_hat", C.c_void_p), ("v_hat", C.c_void_p)]
 
 
 # name -> (restype, argtypes); every symbol include/qfa.h declares
@@ -51,6 +52,7 @@ _I64 = C.c_int64
 SIGNATURES = {
     "qfa_quant_per_token": (C.c_int, [C.c_void_p] * 5 + [_I64] * 8 + [C.c_int, C.c_void_p]),
     "qfa_quant_dequant_per_token": (C.c_int, [C.c_void_p] * 6 + [_I64] * 8 + [C.c_int, C.c_void_p]),
+    "qfa_dequant_per_token": (C.c_int, [C.c_void_p] * 4 + [_I64] * 7 + [C.c_int, C.c_void_p]),
     "qfa_attn_fwd": (C.c_int, [C.POINTER(QfaFwdArgs), C.c_void_p]),
     "qfa_attn_bwd_delta": (C.c_int, [C.c_void_p, C.POINTER(c_i64x3), C.c_void_p, C.POINTER(c_i64x3), C.c_void_p,
                                      _I64, _I64, _I64, _I64, _I64, C.c_int, C.c_void_p]),

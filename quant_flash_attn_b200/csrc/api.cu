@@ -20,6 +20,10 @@ int cuda_fail(cudaError_t e, const char* what) {
 int quant_entry(const void* x, int8_t* codes, uint16_t* scale, int8_t* zp, int32_t* rowsum, void* dequant, int64_t Z,
                 int64_t H, int64_t M, int64_t D, int64_t sz, int64_t sh, int64_t sm, int64_t sk, int dtype,
                 cudaStream_t stream);
+int dequant_entry(const int8_t* codes, const uint16_t* scale, const int8_t* zp, void* out, int64_t Z, int64_t H, int64_t M,
+                  int64_t D, int64_t sz, int64_t sh, int64_t sm, int dtype, cudaStream_t stream);
+int attn_bwd_tc_supported(const QfaBwdArgs& a);
+int attn_bwd_tc_entry(const QfaBwdArgs& a, cudaStream_t stream);
 int attn_fwd_mma_entry(const QfaFwdArgs& a, cudaStream_t stream);
 int attn_fwd_tc_supported(const QfaFwdArgs& a);
 int attn_fwd_tc_entry(const QfaFwdArgs& a, cudaStream_t stream);
@@ -71,6 +75,12 @@ QFA_API int qfa_quant_dequant_per_token(const void* x, int8_t* codes, uint16_t* 
                      dtype, reinterpret_cast<cudaStream_t>(stream));
 }
 
+QFA_API int qfa_dequant_per_token(const int8_t* codes, const uint16_t* scale_f16, const int8_t* zp, void* out, int64_t Z,
+                                  int64_t H, int64_t M, int64_t D, int64_t s_z, int64_t s_h, int64_t s_m, int dtype,
+                                  qfa_stream_t stream) {
+  return dequant_entry(codes, scale_f16, zp, out, Z, H, M, D, s_z, s_h, s_m, dtype, reinterpret_cast<cudaStream_t>(stream));
+}
+
 QFA_API int qfa_attn_fwd(const QfaFwdArgs* a, qfa_stream_t stream) {
   if (!a) return QFA_ERR_NULL;
   int rc = check_common(a->mode, a->dtype, a->B, a->H, a->Sq, a->Skv, a->D);
@@ -110,11 +120,11 @@ QFA_API int qfa_attn_bwd(const QfaBwdArgs* a, qfa_stream_t stream) {
   if (!a) return QFA_ERR_NULL;
   int rc = check_common(a->mode, a->dtype, a->B, a->H, a->Sq, a->Skv, a->D);
   if (rc) return rc;
-  if (!a->d_o || !a->lse || !a->delta || !a->dq || !a->dk || !a->dq_accum) return QFA_ERR_NULL;
+  if (!a->d_o || !a->lse || !a->delta || !a->dq || !a->dk) return QFA_ERR_NULL;
   if (!a->dkv_fused && !a->dv) return QFA_ERR_NULL;
   if (a->lse_stride < a->Sq) return QFA_ERR_STRIDE;
   if (!aligned16(a->d_o) || !strides_mult(a->do_stride, 8) || !aligned16(a->dq) || !strides_mult(a->dq_stride, 8) ||
-      !aligned16(a->dk) || !strides_mult(a->dk_stride, 8) || !aligned16(a->dq_accum))
+      !aligned16(a->dk) || !strides_mult(a->dk_stride, 8))
     return QFA_ERR_ALIGN;
   if (!a->dkv_fused && (!aligned16(a->dv) || !strides_mult(a->dv_stride, 8))) return QFA_ERR_ALIGN;
   if (a->mode == QFA_MODE_REF) {
@@ -127,6 +137,9 @@ QFA_API int qfa_attn_bwd(const QfaBwdArgs* a, qfa_stream_t stream) {
   if ((rc = check_quant_tensor(a->v, false))) return rc;
   if (a->dkv_fused && (a->k.codes != a->v.codes || a->k.scale != a->v.scale || a->k.zp != a->v.zp)) return QFA_ERR_MODE;
   if (attn_bwd_shortq_supported(*a)) return attn_bwd_shortq_entry(*a, reinterpret_cast<cudaStream_t>(stream));
+  if (attn_bwd_tc_supported(*a)) return attn_bwd_tc_entry(*a, reinterpret_cast<cudaStream_t>(stream));
+  if (!a->dq_accum) return QFA_ERR_NULL;
+  if (!aligned16(a->dq_accum)) return QFA_ERR_ALIGN;
   return attn_bwd_mma_entry(*a, a->dq_accum, reinterpret_cast<cudaStream_t>(stream));
 }
 
@@ -148,7 +161,7 @@ QFA_API const char* qfa_strerror(int code) {
 }
 
 QFA_API const char* qfa_last_cuda_error(void) { return g_cuda_err; }
-QFA_API int qfa_version(void) { return 1; }
+QFA_API int qfa_version(void) { return 2; }
 QFA_API int64_t qfa_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 }  // extern "C"

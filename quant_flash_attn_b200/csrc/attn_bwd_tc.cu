@@ -1,0 +1,517 @@
+// INT8 flash-attention backward on tcgen05 (sm_100a), int8 mode.
+//
+// Two launches of ONE kernel template, following the split of the FA2 tutorial the reference ships
+// (flash_attn_triton.py:393-435: a dK/dV pass, then a dQ pass, each recomputing P):
+//
+//   pass KV (rows = a 128-token K/V tile, walks the query tiles)      pass Q (rows = a 128-row query tile, walks K/V tiles)
+//     T1 = Kc Qc^T          int8 kind::i8                               T1 = Qc Kc^T
+//     T2 = V^ dO^T          kind::f16, both operands K-major            T2 = dO V^^T
+//     P^T  = exp2(logit - LSE)              (quant_flash_attn.py:153-155)  P  = ...
+//     dS^T = P^T * (T2 - delta)             (quant_flash_attn.py:157-158)  dS = ...
+//     dV += P^T dO          P^T read from tensor memory                 --
+//     dK += dS^T Q^         dS^T read from tensor memory                dQ += dS K^
+//
+// "rows" live in tensor-memory lanes, so the same code serves both passes with the roles of the row-side
+// (stationary: codes + one 16-bit tensor, loaded once) and column-side (streamed by TMA, double buffered)
+// operands swapped.  Logits come from the same int8 product + zero-point correction as the forward, so the
+// recomputed P matches the saved LSE; Q^, K^, V^ are the dequantized 16-bit operands (straight-through
+// gradients).  Tensor memory: T1 | T2 | acc1 | acc2 = 128 + 128 + D + D columns; P / dS are written back as
+// packed 16-bit into the first halves of T1 / T2.
+// Warp roles as in the forward: producer, MMA issuer, tensor-memory allocator, four softmax warps reading in the
+// 16x256b fragment layout (a thread owns 4 rows x 32 columns; the five per-column constants are loaded once per
+// four rows).  All waits are time-bounded.
+#include <atomic>
+#include <type_traits>
+
+#include "qfa_common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace qfa {
+
+using namespace sm100;
+
+struct TcBwdParams {
+  // row side (per token of the stationary tile) and column side (per token of the streamed tiles)
+  const uint16_t* r_scale; const int8_t* r_zp; const int32_t* r_sum;
+  const uint16_t* c_scale; const int8_t* c_zp; const int32_t* c_sum;
+  const float* lse;      // per query row, natural log
+  const float* delta;    // per query row
+  int64_t lse_stride;
+  void* out1; int64_t out1_stride[3];    // pass KV: dV      pass Q: unused
+  void* out2; int64_t out2_stride[3];    // pass KV: dK      pass Q: dQ
+  int H, rows_total, cols_total;         // pass KV: rows = Skv, cols = Sq;  pass Q: rows = Sq, cols = Skv
+  float sm_scale;
+  int causal;
+  unsigned int epoch;
+  int32_t* status;
+};
+
+template <int D>
+struct BwdTcCfg {
+  static constexpr int BM = 128, BN = 128, STAGES = 2;
+  static constexpr int C_BYTES = 128 * D;              // int8 tile
+  static constexpr int H_BYTES = 128 * D * 2;          // 16-bit tile
+  static constexpr int PANELS = D / 64;
+  static constexpr int PANEL_BYTES = 128 * 128;
+  static constexpr int M_BYTES = 128 * 5 * 4;          // per column: z, -sum, s, -lse*log2e, -delta
+  static constexpr int XC_OFF = 0;
+  static constexpr int XH_OFF = XC_OFF + C_BYTES;
+  static constexpr int ST_OFF = XH_OFF + H_BYTES;                      // stages: [Yc | Ya | Yb]
+  static constexpr int ST_BYTES = C_BYTES + 2 * H_BYTES;
+  static constexpr int M_OFF = ST_OFF + STAGES * ST_BYTES;
+  static constexpr int BAR_OFF = M_OFF + STAGES * M_BYTES;
+  static constexpr int NBARS = 1 + 3 * STAGES + 4;
+  static constexpr int MISC_OFF = BAR_OFF + NBARS * 8;
+  static constexpr int SMEM = MISC_OFF + 16 + 1024;
+  static constexpr int THREADS = 256;
+  static constexpr int T1_COL = 0, T2_COL = 128, ACC1_COL = 256, ACC2_COL = 256 + D;
+  static constexpr int TMEM_COLS = 512;
+  static_assert(SMEM <= 232448, "shared memory budget");
+};
+
+struct BwdRow4 {
+  float2 a2[4], A2[4], z2[4], nlse2[4], ndelta2[4];
+};
+
+// One block of 32 columns for the four rows of a thread: T1 fragments (int32 logits) + T2 fragments (fp32 dP)
+// -> P and dS packed to 16 bit in the 16x128b store layout.  KV_PASS: LSE / delta belong to the columns
+// (queries) and the causal mask hides columns BELOW the row; otherwise they belong to the rows and the mask
+// hides columns ABOVE the row.
+template <typename T, bool KV_PASS, bool MASKED>
+__device__ __forceinline__ void bwd_block(const uint32_t (&sA)[16], const uint32_t (&sB)[16], const uint32_t (&dA)[16],
+                                          const uint32_t (&dB)[16], const float* meta, const int (&lo)[4],
+                                          const int (&hi)[4], const BwdRow4& rc, uint32_t* pA, uint32_t* pB,
+                                          uint32_t* gA, uint32_t* gB) {
+  using H16 = Half16<T>;
+  const float2 negM2 = make_float2(-12582912.0f, -12582912.0f);
+#pragma unroll
+  for (int n = 0; n < 4; ++n) {
+    const float2 z2 = *reinterpret_cast<const float2*>(meta + 8 * n);
+    const float2 n2 = *reinterpret_cast<const float2*>(meta + 128 + 8 * n);
+    const float2 s2 = *reinterpret_cast<const float2*>(meta + 256 + 8 * n);
+    float2 l2 = make_float2(0.f, 0.f), d2 = make_float2(0.f, 0.f);
+    if (KV_PASS) {
+      l2 = *reinterpret_cast<const float2*>(meta + 384 + 8 * n);
+      d2 = *reinterpret_cast<const float2*>(meta + 512 + 8 * n);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int i0 = 4 * n + 2 * (k & 1);
+      const uint32_t s0 = (k < 2) ? sA[i0] : sB[i0], s1 = (k < 2) ? sA[i0 + 1] : sB[i0 + 1];
+      const uint32_t g0 = (k < 2) ? dA[i0] : dB[i0], g1 = (k < 2) ? dA[i0 + 1] : dB[i0 + 1];
+      // exact integer logits (see the forward kernel), then scale and subtract the saved LSE
+      float2 v = make_float2(__uint_as_float(s0 + 0x4B400000u), __uint_as_float(s1 + 0x4B400000u));
+      v = __fadd2_rn(v, negM2);
+      v = __ffma2_rn(z2, rc.A2[k], v);
+      v = __ffma2_rn(n2, rc.z2[k], v);
+      v = __fmul2_rn(v, s2);
+      v = __ffma2_rn(v, rc.a2[k], KV_PASS ? l2 : rc.nlse2[k]);
+      if (MASKED) {
+        // visible columns of row k inside this block: lo[k] <= 8n + e < hi[k]
+        if (8 * n < lo[k] || 8 * n >= hi[k]) v.x = -INFINITY;
+        if (8 * n + 1 < lo[k] || 8 * n + 1 >= hi[k]) v.y = -INFINITY;
+      }
+      const float p0 = fast_exp2(v.x), p1 = fast_exp2(v.y);
+      float2 dd = __fadd2_rn(make_float2(__uint_as_float(g0), __uint_as_float(g1)), KV_PASS ? d2 : rc.ndelta2[k]);
+      dd = __fmul2_rn(make_float2(p0, p1), dd);
+      const uint32_t wp = H16::pack(p0, p1);          // P rounded to 16 bit (quant_flash_attn.py:156)
+      const uint32_t wd = H16::pack(dd.x, dd.y);      // dS rounded to 16 bit (quant_flash_attn.py:159-160)
+      if (k < 2) { pA[2 * n + (k & 1)] = wp; gA[2 * n + (k & 1)] = wd; }
+      else { pB[2 * n + (k & 1)] = wp; gB[2 * n + (k & 1)] = wd; }
+    }
+  }
+}
+
+template <typename T, int D, bool KV_PASS>
+__global__ void __launch_bounds__(256, 1)
+attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_constant__ CUtensorMap tmXh,
+                   const __grid_constant__ CUtensorMap tmYc, const __grid_constant__ CUtensorMap tmYa,
+                   const __grid_constant__ CUtensorMap tmYb, const TcBwdParams p) {
+  using C = BwdTcCfg<D>;
+  using H16 = Half16<T>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t sbase = smem_u32(smem);
+  auto BAR = [&](int i) { return sbase + C::BAR_OFF + 8u * i; };
+  constexpr int B_XFULL = 0;
+  constexpr int B_YFULL = 1, B_YEMPTY = B_YFULL + C::STAGES, B_MFULL = B_YEMPTY + C::STAGES;
+  constexpr int B_T1 = B_MFULL + C::STAGES, B_T2 = B_T1 + 1, B_PD = B_T2 + 1, B_ACC = B_PD + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::MISC_OFF);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::MISC_OFF + 4);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int r_blocks = (p.rows_total + C::BM - 1) / C::BM;
+  const int c_blocks = (p.cols_total + C::BN - 1) / C::BN;
+  const int bh = blockIdx.x / r_blocks;
+  const int b = bh / p.H, h = bh % p.H;
+  const int rrank = blockIdx.x % r_blocks;
+  // heavy row blocks first under the causal mask: early K/V tiles (pass KV), late query tiles (pass Q)
+  const int rblk = (p.causal && !KV_PASS) ? (r_blocks - 1 - rrank) : rrank;
+  const int r0 = rblk * C::BM;
+  // column tiles this row block meets
+  int j_begin = 0, j_end = c_blocks;
+  if (p.causal) {
+    if (KV_PASS) j_begin = r0 / C::BN;                                   // queries >= first token of the tile
+    else j_end = min(c_blocks, (r0 + C::BM + C::BN - 1) / C::BN);        // tokens <= last query of the tile
+  }
+  const int n_steps = max(0, j_end - j_begin);
+
+  if (tid == 0) {
+    *abort_flag = launch_aborted(p.epoch) ? 1 : 0;
+    mbar_init(BAR(B_XFULL), 1);
+    for (int i = 0; i < C::STAGES; ++i) {
+      mbar_init(BAR(B_YFULL + i), 1);
+      mbar_init(BAR(B_YEMPTY + i), 1);
+      mbar_init(BAR(B_MFULL + i), 32);
+    }
+    mbar_init(BAR(B_T1), 1);
+    mbar_init(BAR(B_T2), 1);
+    mbar_init(BAR(B_PD), 128);
+    mbar_init(BAR(B_ACC), 1);
+    fence_barrier_init();
+  }
+  if (warp == 2) {
+    tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  const int64_t tok_r0 = static_cast<int64_t>(bh) * p.rows_total;
+  const int64_t tok_c0 = static_cast<int64_t>(bh) * p.cols_total;
+  // queries index LSE / delta: they are the columns in pass KV, the rows in pass Q
+  const int64_t lse0 = static_cast<int64_t>(bh) * p.lse_stride;
+
+  if (warp == 0) {
+    // ================================================================ producer
+    if (lane == 0) {
+      prefetch_tmap(&tmXc); prefetch_tmap(&tmXh); prefetch_tmap(&tmYc); prefetch_tmap(&tmYa); prefetch_tmap(&tmYb);
+      mbar_arrive_expect_tx(BAR(B_XFULL), C::C_BYTES + C::H_BYTES);
+      tma_load_4d(sbase + C::XC_OFF, &tmXc, BAR(B_XFULL), 0, r0, h, b);
+      for (int pn = 0; pn < C::PANELS; ++pn)
+        tma_load_4d(sbase + C::XH_OFF + pn * C::PANEL_BYTES, &tmXh, BAR(B_XFULL), pn * 64, r0, h, b);
+    }
+    bool ok = true;
+    for (int it = 0; it < n_steps && ok; ++it) {
+      const int c0 = (j_begin + it) * C::BN;
+      const int st = it % C::STAGES;
+      ok = mbar_wait(BAR(B_YEMPTY + st), ((it / C::STAGES) & 1) ^ 1, abort_flag, p.epoch);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const uint32_t stage = sbase + C::ST_OFF + st * C::ST_BYTES;
+      if (lane == 0) {
+        mbar_arrive_expect_tx(BAR(B_YFULL + st), C::ST_BYTES);
+        tma_load_4d(stage, &tmYc, BAR(B_YFULL + st), 0, c0, h, b);
+        for (int pn = 0; pn < C::PANELS; ++pn) {
+          tma_load_4d(stage + C::C_BYTES + pn * C::PANEL_BYTES, &tmYa, BAR(B_YFULL + st), pn * 64, c0, h, b);
+          tma_load_4d(stage + C::C_BYTES + C::H_BYTES + pn * C::PANEL_BYTES, &tmYb, BAR(B_YFULL + st), pn * 64, c0, h, b);
+        }
+      }
+      // per-column constants (the stage's previous readers are done: Y-empty is committed after the step's last MMA,
+      // which is issued after the softmax warps finished the step)
+      float* meta = reinterpret_cast<float*>(smem + C::M_OFF + st * C::M_BYTES);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int col = i * 32 + lane;
+        const int c = c0 + col;
+        float z = 0.f, ns = 0.f, s = 0.f, nl = -INFINITY, nd = 0.f;
+        if (c < p.cols_total) {
+          s = half_bits_to_f32(p.c_scale[tok_c0 + c]);
+          z = static_cast<float>(p.c_zp[tok_c0 + c]);
+          ns = -static_cast<float>(p.c_sum[tok_c0 + c]);
+          nl = 0.f;
+          if (KV_PASS) {
+            nl = -p.lse[lse0 + c] * kLog2e;
+            nd = -p.delta[lse0 + c];
+          }
+        }
+        meta[col] = z;
+        meta[128 + col] = ns;
+        meta[256 + col] = s;
+        meta[384 + col] = nl;      // columns past the end: -inf reference -> P = 0 (pass Q masks them by index)
+        meta[512 + col] = nd;
+      }
+      mbar_arrive(BAR(B_MFULL + st));
+    }
+  } else if (warp == 1) {
+    // ================================================================ MMA issuer (one thread)
+    if (lane == 0) {
+      constexpr uint32_t kIdescT1 = make_idesc(2, 1, 1, 0, 0, 128, 128);
+      constexpr uint32_t kF = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+      constexpr uint32_t kIdescT2 = make_idesc(1, kF, kF, 0, 0, 128, 128);       // both operands K-major
+      constexpr uint32_t kIdescAcc = make_idesc(1, kF, kF, 0, 1, 128, D);        // B MN-major
+      constexpr uint64_t kCSwz = (D == 128) ? kSwizzle128B : kSwizzle64B;
+      bool ok = mbar_wait(BAR(B_XFULL), 0, abort_flag, p.epoch);
+      tc_fence_after_sync();
+      for (int it = 0; it < n_steps && ok; ++it) {
+        const int st = it % C::STAGES;
+        const uint32_t stage = sbase + C::ST_OFF + st * C::ST_BYTES;
+        ok = mbar_wait(BAR(B_YFULL + st), (it / C::STAGES) & 1, abort_flag, p.epoch);
+        if (!ok) break;
+        tc_fence_after_sync();
+        // T1 = Xc Yc^T (int8), T2 = Xh Ya^T (16 bit, K-major x K-major)
+        {
+          const uint64_t da = make_smem_desc(sbase + C::XC_OFF, 16, 8 * D, kCSwz);
+          const uint64_t db = make_smem_desc(stage, 16, 8 * D, kCSwz);
+#pragma unroll
+          for (int k = 0; k < D / 32; ++k)
+            mma_i8_ss(tmem + C::T1_COL, desc_advance(da, k * 32), desc_advance(db, k * 32), kIdescT1, k > 0);
+          mma_commit(BAR(B_T1));
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k) {
+            const uint32_t off = (k / 4) * C::PANEL_BYTES + (k % 4) * 32;
+            const uint64_t ha = make_smem_desc(sbase + C::XH_OFF + off, 16, 1024, kSwizzle128B);
+            const uint64_t hb = make_smem_desc(stage + C::C_BYTES + off, 16, 1024, kSwizzle128B);
+            mma_f16_ss(tmem + C::T2_COL, ha, hb, kIdescT2, k > 0);
+          }
+          mma_commit(BAR(B_T2));
+        }
+        // accumulate with P / dS read from tensor memory
+        ok = mbar_wait(BAR(B_PD), it & 1, abort_flag, p.epoch);
+        if (!ok) break;
+        tc_fence_after_sync();
+        if (KV_PASS) {
+          // acc1 (dV) += P^T dO : right operand = the Ya tile (dO) viewed MN-major
+          const uint64_t db = make_smem_desc(stage + C::C_BYTES, C::PANEL_BYTES, 1024, kSwizzle128B);
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            mma_f16_ts(tmem + C::ACC1_COL, tmem + C::T1_COL + k * 8, desc_advance(db, k * 2048), kIdescAcc,
+                       (it > 0 || k > 0) ? 1u : 0u);
+        }
+        {
+          // acc2 (dK or dQ) += dS Yb : Yb = Q^ (pass KV) or K^ (pass Q), MN-major
+          const uint64_t db = make_smem_desc(stage + C::C_BYTES + C::H_BYTES, C::PANEL_BYTES, 1024, kSwizzle128B);
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            mma_f16_ts(tmem + C::ACC2_COL, tmem + C::T2_COL + k * 8, desc_advance(db, k * 2048), kIdescAcc,
+                       (it > 0 || k > 0) ? 1u : 0u);
+        }
+        mma_commit(BAR(B_YEMPTY + st));
+        if (it == n_steps - 1) mma_commit(BAR(B_ACC));
+      }
+    }
+  } else if (warp >= 4) {
+    // ================================================================ softmax-side math
+    const int wq = warp & 3;
+    const int g = lane >> 2, q = lane & 3;
+    const uint32_t quarter = static_cast<uint32_t>(wq * 32) << 16;
+    constexpr uint32_t kLane16 = 16u << 16;
+    const uint32_t tT1 = tmem + quarter + C::T1_COL, tT2 = tmem + quarter + C::T2_COL;
+    int rowk[4];
+    BwdRow4 rc;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      rowk[k] = r0 + wq * 32 + g + 8 * k;
+      float A = 0.f, z = 0.f, a = 0.f, nl = -INFINITY, nd = 0.f;
+      if (rowk[k] < p.rows_total) {
+        const int64_t tk = tok_r0 + rowk[k];
+        const int zi = p.r_zp[tk];
+        z = static_cast<float>(zi);
+        A = static_cast<float>(D * zi - p.r_sum[tk]);
+        a = half_bits_to_f32(p.r_scale[tk]) * p.sm_scale * kLog2e;
+        nl = 0.f;
+        if (!KV_PASS) {
+          nl = -p.lse[lse0 + rowk[k]] * kLog2e;
+          nd = -p.delta[lse0 + rowk[k]];
+        }
+      }
+      rc.a2[k] = make_float2(a, a);
+      rc.A2[k] = make_float2(A, A);
+      rc.z2[k] = make_float2(z, z);
+      rc.nlse2[k] = make_float2(nl, nl);        // rows past the end: -inf -> P = 0
+      rc.ndelta2[k] = make_float2(nd, nd);
+    }
+    bool ok = true;
+    for (int it = 0; it < n_steps && ok; ++it) {
+      const int st = it % C::STAGES;
+      const int c0 = (j_begin + it) * C::BN;
+      ok = mbar_wait(BAR(B_MFULL + st), (it / C::STAGES) & 1, abort_flag, p.epoch);
+      if (ok) ok = mbar_wait(BAR(B_T1), it & 1, abort_flag, p.epoch);
+      if (ok) ok = mbar_wait(BAR(B_T2), it & 1, abort_flag, p.epoch);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const float* meta = reinterpret_cast<const float*>(smem + C::M_OFF + st * C::M_BYTES) + 2 * q;
+      // visible column range of each row, relative to (tile start + 2q)
+      int lo[4], hi[4];
+      bool any_masked = false;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        int first = 0, last = p.cols_total - c0;                  // [first, last) in tile coordinates
+        if (p.causal) {
+          if (KV_PASS) first = max(first, rowk[k] - c0);          // query >= token
+          else last = min(last, rowk[k] + 1 - c0);                // token <= query
+        }
+        any_masked |= (first > 0) || (last < C::BN);
+        lo[k] = first - 2 * q;
+        hi[k] = last - 2 * q;
+      }
+      const bool masked = __any_sync(0xffffffffu, any_masked);
+#pragma unroll
+      for (int blk = 0; blk < 4; ++blk) {
+        uint32_t sA[16], sB[16], dA[16], dB[16];
+        tmem_ld_16x256b_x4(tT1 + blk * 32, sA);
+        tmem_ld_16x256b_x4(tT1 + kLane16 + blk * 32, sB);
+        tmem_ld_16x256b_x4(tT2 + blk * 32, dA);
+        tmem_ld_16x256b_x4(tT2 + kLane16 + blk * 32, dB);
+        tmem_wait_ld();
+        int lo_b[4], hi_b[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { lo_b[k] = lo[k] - blk * 32; hi_b[k] = hi[k] - blk * 32; }
+        uint32_t pA[8], pB[8], gA[8], gB[8];
+        if (masked) bwd_block<T, KV_PASS, true>(sA, sB, dA, dB, meta + blk * 32, lo_b, hi_b, rc, pA, pB, gA, gB);
+        else bwd_block<T, KV_PASS, false>(sA, sB, dA, dB, meta + blk * 32, lo_b, hi_b, rc, pA, pB, gA, gB);
+        // P / dS of this block go to columns [16 blk, 16 blk + 16) of T1 / T2: already consumed above
+        asm volatile("tcgen05.st.sync.aligned.16x128b.x4.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                     ::"r"(tT1 + blk * 16), "r"(pA[0]), "r"(pA[1]), "r"(pA[2]), "r"(pA[3]), "r"(pA[4]), "r"(pA[5]),
+                       "r"(pA[6]), "r"(pA[7]) : "memory");
+        asm volatile("tcgen05.st.sync.aligned.16x128b.x4.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                     ::"r"(tT1 + kLane16 + blk * 16), "r"(pB[0]), "r"(pB[1]), "r"(pB[2]), "r"(pB[3]), "r"(pB[4]),
+                       "r"(pB[5]), "r"(pB[6]), "r"(pB[7]) : "memory");
+        asm volatile("tcgen05.st.sync.aligned.16x128b.x4.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                     ::"r"(tT2 + blk * 16), "r"(gA[0]), "r"(gA[1]), "r"(gA[2]), "r"(gA[3]), "r"(gA[4]), "r"(gA[5]),
+                       "r"(gA[6]), "r"(gA[7]) : "memory");
+        asm volatile("tcgen05.st.sync.aligned.16x128b.x4.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                     ::"r"(tT2 + kLane16 + blk * 16), "r"(gB[0]), "r"(gB[1]), "r"(gB[2]), "r"(gB[3]), "r"(gB[4]),
+                       "r"(gB[5]), "r"(gB[6]), "r"(gB[7]) : "memory");
+      }
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(BAR(B_PD));
+    }
+    // ---------------- epilogue: accumulators -> 16 bit.  dK and dQ carry sm_scale (quant_flash_attn.py:161,164)
+    if (ok && n_steps > 0) {
+      ok = mbar_wait(BAR(B_ACC), 0, abort_flag, p.epoch);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after_sync();
+      const int row = r0 + wq * 32 + lane;
+      for (int which = KV_PASS ? 0 : 1; which < 2; ++which) {
+        const uint32_t tA = tmem + quarter + (which == 0 ? C::ACC1_COL : C::ACC2_COL);
+        const float scale = (which == 0) ? 1.0f : p.sm_scale;
+        const int64_t* os = (which == 0) ? p.out1_stride : p.out2_stride;
+        T* orow = static_cast<T*>(which == 0 ? p.out1 : p.out2) + b * os[0] + h * os[1] + static_cast<int64_t>(row) * os[2];
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t oreg[32];
+          if (n_steps > 0) {
+            tmem_ld32(tA + c * 32, oreg);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) oreg[i] = 0u;       // a row block that meets no column tile: zero gradient
+          }
+          if (row < p.rows_total) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 v;
+              v.x = H16::pack(__uint_as_float(oreg[i]) * scale, __uint_as_float(oreg[i + 1]) * scale);
+              v.y = H16::pack(__uint_as_float(oreg[i + 2]) * scale, __uint_as_float(oreg[i + 3]) * scale);
+              v.z = H16::pack(__uint_as_float(oreg[i + 4]) * scale, __uint_as_float(oreg[i + 5]) * scale);
+              v.w = H16::pack(__uint_as_float(oreg[i + 6]) * scale, __uint_as_float(oreg[i + 7]) * scale);
+              *reinterpret_cast<uint4*>(orow + c * 32 + i) = v;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, C::TMEM_COLS);
+  }
+  if (tid == 0 && *abort_flag && p.status) *p.status = QFA_STATUS_WAIT_TIMEOUT;
+}
+
+static std::atomic<unsigned int> g_bwd_epoch{0x40000000u};
+
+template <typename T, int D, bool KV_PASS>
+static int launch_bwd_tc(const QfaBwdArgs& a, cudaStream_t stream) {
+  using C = BwdTcCfg<D>;
+  const CUtensorMapSwizzle cswz = (D == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  const CUtensorMapDataType hdt =
+      std::is_same<T, __nv_bfloat16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  // row side / column side operands
+  const QfaQuantTensor& X = KV_PASS ? a.k : a.qq;
+  const QfaQuantTensor& Y = KV_PASS ? a.qq : a.k;
+  const int64_t Sx = KV_PASS ? a.Skv : a.Sq, Sy = KV_PASS ? a.Sq : a.Skv;
+  const void* xh = KV_PASS ? a.v_hat : a.d_o;          // stationary 16-bit operand of T2
+  const void* ya = KV_PASS ? a.d_o : a.v_hat;          // streamed 16-bit operand of T2 (also B of acc1 in pass KV)
+  const void* yb = KV_PASS ? a.q_hat : a.k_hat;        // streamed MN-major operand of acc2
+  auto map16 = [&](CUtensorMap* m, const void* base, int64_t S, const int64_t* stride_or_null) {
+    // contiguous (B,H,S,D) unless strides are given (dO)
+    const uint64_t ss = stride_or_null ? 2ull * stride_or_null[2] : 2ull * D;
+    const uint64_t sh = stride_or_null ? 2ull * stride_or_null[1] : 2ull * D * S;
+    const uint64_t sb = stride_or_null ? 2ull * stride_or_null[0] : 2ull * D * S * a.H;
+    return make_tmap_4d(m, base, hdt, 2, D, S, a.H, a.B, ss, sh, sb, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+  };
+  CUtensorMap tmXc, tmXh, tmYc, tmYa, tmYb;
+  bool ok = make_tmap_4d(&tmXc, X.codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, D, Sx, a.H, a.B, X.stride[2], X.stride[1],
+                         X.stride[0], D, 128, cswz);
+  ok = ok && make_tmap_4d(&tmYc, Y.codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, D, Sy, a.H, a.B, Y.stride[2], Y.stride[1],
+                          Y.stride[0], D, 128, cswz);
+  ok = ok && map16(&tmXh, xh, Sx, KV_PASS ? nullptr : a.do_stride);
+  ok = ok && map16(&tmYa, ya, Sy, KV_PASS ? a.do_stride : nullptr);
+  ok = ok && map16(&tmYb, yb, Sy, nullptr);
+  if (!ok) return cuda_fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
+  TcBwdParams p;
+  p.r_scale = X.scale; p.r_zp = X.zp; p.r_sum = X.rowsum;
+  p.c_scale = Y.scale; p.c_zp = Y.zp; p.c_sum = Y.rowsum;
+  p.lse = a.lse; p.delta = a.delta; p.lse_stride = a.lse_stride;
+  p.out1 = KV_PASS ? a.dv : nullptr;
+  p.out2 = KV_PASS ? a.dk : a.dq;
+  for (int i = 0; i < 3; ++i) {
+    p.out1_stride[i] = KV_PASS ? a.dv_stride[i] : 0;
+    p.out2_stride[i] = KV_PASS ? a.dk_stride[i] : a.dq_stride[i];
+  }
+  p.H = static_cast<int>(a.H);
+  p.rows_total = static_cast<int>(Sx);
+  p.cols_total = static_cast<int>(Sy);
+  p.sm_scale = a.sm_scale; p.causal = a.causal; p.status = a.status;
+  p.epoch = g_bwd_epoch.fetch_add(1, std::memory_order_relaxed) + 1;
+  auto kern = attn_bwd_tc_kernel<T, D, KV_PASS>;
+  static bool attr_done[64] = {};
+  int devid = 0;
+  QFA_CUDA_TRY(cudaGetDevice(&devid));
+  if (devid < 64 && !attr_done[devid]) {
+    QFA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+    attr_done[devid] = true;
+  }
+  const int64_t n_ctas = ((Sx + C::BM - 1) / C::BM) * a.B * a.H;
+  if (n_ctas > 0x7fffffffLL) return QFA_ERR_SHAPE;
+  kern<<<static_cast<unsigned>(n_ctas), C::THREADS, C::SMEM, stream>>>(tmXc, tmXh, tmYc, tmYa, tmYb, p);
+  note_launch();
+  QFA_CUDA_TRY(cudaGetLastError());
+  return QFA_OK;
+}
+
+int attn_bwd_tc_supported(const QfaBwdArgs& a) {
+  if (a.mode != QFA_MODE_INT8 || a.dkv_fused) return 0;
+  if (!a.q_hat || !a.k_hat || !a.v_hat) return 0;
+  if (a.D != 128 && a.D != 64) return 0;
+  if (!(a.sm_scale > 0.f)) return 0;
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (!al(a.q_hat) || !al(a.k_hat) || !al(a.v_hat)) return 0;
+  if (a.do_stride[0] % 8 || a.do_stride[1] % 8 || a.do_stride[2] % 8) return 0;
+  return 1;
+}
+
+int attn_bwd_tc_entry(const QfaBwdArgs& a, cudaStream_t stream) {
+  const bool bf = a.dtype == QFA_BF16;
+  int rc;
+  if (a.D == 128) {
+    rc = bf ? launch_bwd_tc<__nv_bfloat16, 128, true>(a, stream) : launch_bwd_tc<__half, 128, true>(a, stream);
+    if (rc) return rc;
+    return bf ? launch_bwd_tc<__nv_bfloat16, 128, false>(a, stream) : launch_bwd_tc<__half, 128, false>(a, stream);
+  }
+  rc = bf ? launch_bwd_tc<__nv_bfloat16, 64, true>(a, stream) : launch_bwd_tc<__half, 64, true>(a, stream);
+  if (rc) return rc;
+  return bf ? launch_bwd_tc<__nv_bfloat16, 64, false>(a, stream) : launch_bwd_tc<__half, 64, false>(a, stream);
+}
+
+}  // namespace qfa

@@ -65,5 +65,6 @@ extern "C" QFA_API int qfa_attn_bwd_static_scratch(const QfaBwdArgs* a, qfa_stre
   // call's contents otherwise).
   QfaBwdArgs b = *a;
   b.dq_accum = scratch;
+  b.q_hat = b.k_hat = b.v_hat = nullptr;   // always the kernel that accumulates dQ in scratch memory
   return qfa_attn_bwd(&b, stream);
 }

@@ -167,6 +167,19 @@ def int8_attention_forward(qq, kq, vq, causal: bool, sm_scale: float, dtype: tor
     return o, lse
 
 
+def dequantize_16bit(codes, scale, zp, dtype: torch.dtype) -> torch.Tensor:
+    """(code - zp) * scale rounded to `dtype` as a contiguous (B,H,S,D) tensor (quant_flash_attn.py:65-66)."""
+    B, H, S, D = codes.shape
+    codes = _rows16(codes)
+    out = torch.empty((B, H, S, D), dtype=dtype, device=codes.device)
+    with torch.cuda.device(codes.device):
+        rc = _lib.load().qfa_dequant_per_token(codes.data_ptr(), _flat(scale).data_ptr(), _flat(zp).data_ptr(),
+                                               out.data_ptr(), B, H, S, D, codes.stride(0), codes.stride(1),
+                                               codes.stride(2), _DT[dtype], _stream(codes))
+    _lib.check(rc, "qfa_dequant_per_token")
+    return out
+
+
 def int8_attention_backward(qq, kq, vq, causal, sm_scale, o, lse, do):
     """Backward of the int8 operator; returns (dq, dk, dv) in o's dtype."""
     qc, qs, qz, qsum = qq[:4]
@@ -180,9 +193,19 @@ def int8_attention_backward(qq, kq, vq, causal, sm_scale, o, lse, do):
     dk = torch.empty((B, H, Skv, D), dtype=dtype, device=dev)
     dv = torch.empty((B, H, Skv, D), dtype=dtype, device=dev)
     delta = torch.empty((B, H, Sq), dtype=torch.float32, device=dev)
-    dq_accum = torch.empty((B, H, Sq, D), dtype=torch.float32, device=dev)
+    # the tcgen05 kernels take the dequantized operands as 16-bit tensors and need no dQ scratch; the
+    # general kernel (non-positive sm_scale) accumulates dQ in fp32 scratch instead
+    use_tc = float(sm_scale) > 0.0
+    q_hat = k_hat = v_hat = dq_accum = None
+    if use_tc:
+        q_hat = dequantize_16bit(qc, qs, qz, dtype)
+        k_hat = dequantize_16bit(kc, ks, kz, dtype)
+        v_hat = vq[4] if len(vq) > 4 and vq[4] is not None else dequantize_16bit(vc, vs, vz, dtype)
+    else:
+        dq_accum = torch.empty((B, H, Sq, D), dtype=torch.float32, device=dev)
     lib = _lib.load()
     stream = _stream(qc)
+    status = torch.zeros(1, dtype=torch.int32, device=dev) if os.environ.get("QFA_CHECK_STATUS") else None
     with torch.cuda.device(dev):
         so, sdo = _s3(o), _s3(do)
         rc = lib.qfa_attn_bwd_delta(o.data_ptr(), C.byref(so), do.data_ptr(), C.byref(sdo), delta.data_ptr(),
@@ -194,9 +217,17 @@ def int8_attention_backward(qq, kq, vq, causal, sm_scale, o, lse, do):
             qq=_quant_tensor(qc, qs, qz, qsum), k=_quant_tensor(kc, ks, kz, ksum), v=_quant_tensor(vc, vs, vz),
             d_o=do.data_ptr(), do_stride=sdo, lse=lse.data_ptr(), delta=delta.data_ptr(), lse_stride=Sq,
             dq=dq.data_ptr(), dq_stride=_s3(dq), dk=dk.data_ptr(), dk_stride=_s3(dk),
-            dv=dv.data_ptr(), dv_stride=_s3(dv), dq_accum=dq_accum.data_ptr(), status=None)
+            dv=dv.data_ptr(), dv_stride=_s3(dv),
+            dq_accum=dq_accum.data_ptr() if dq_accum is not None else None,
+            status=status.data_ptr() if status is not None else None,
+            q_hat=q_hat.data_ptr() if use_tc else None, k_hat=k_hat.data_ptr() if use_tc else None,
+            v_hat=v_hat.data_ptr() if use_tc else None)
         rc = lib.qfa_attn_bwd(C.byref(args), stream)
     _lib.check(rc, "qfa_attn_bwd")
+    if status is not None:
+        code = int(status.item())
+        if code:
+            raise RuntimeError(f"qfa_attn_bwd kernel status {code}: {lib.qfa_strerror(code).decode()}")
     return dq, dk, dv
 
 
@@ -214,7 +245,7 @@ class QuantAttention(torch.autograd.Function):
             raise ValueError("expected q (B,H,Sq,D) and k, v (B,H,Skv,D)")
         qq, kq, vq = quantize_qkv(q, k, v)
         o, lse = int8_attention_forward(qq, kq, vq, causal, sm_scale, q.dtype)
-        ctx.save_for_backward(o, lse, *qq[:4], *kq[:4], *vq[:3])
+        ctx.save_for_backward(o, lse, *qq[:4], *kq[:4], *vq[:3], vq[4])
         ctx.causal, ctx.sm_scale = bool(causal), float(sm_scale)
         return o
 
@@ -222,7 +253,7 @@ class QuantAttention(torch.autograd.Function):
     def backward(ctx, grad_output):
         t = ctx.saved_tensors
         o, lse = t[0], t[1]
-        qq, kq, vq = t[2:6], t[6:10], t[10:13]
+        qq, kq, vq = t[2:6], t[6:10], (t[10], t[11], t[12], None, t[13])
         dq, dk, dv = int8_attention_backward(qq, kq, vq, ctx.causal, ctx.sm_scale, o, lse, grad_output)
         return dq, dk, dv, None, None
 

@@ -46,8 +46,12 @@ def test_static_scratch_backward_matches_allocating_backward():
     # two different problems back to back: the second must not see the first one's accumulator
     for call, (B, H, S, D, causal) in enumerate([(2, 4, 512, 128, True), (1, 3, 700, 64, False)]):
         qq, kq, vq, o, lse, do, sm = _problem(qfa, B, H, S, D, causal, seed=100 + call)
-        want = qfa.int8_attention_backward(qq, kq, vq, causal, sm, o, lse, do)     # existing entry point
         delta = (o.float() * do.float()).sum(-1).contiguous()
+        # existing entry point (qfa_attn_bwd) on the same kernel: caller-allocated fp32 accumulator
+        want = tuple(torch.empty(B, H, S, D, device="cuda", dtype=torch.bfloat16) for _ in range(3))
+        accum = torch.empty(B, H, S, D, device="cuda", dtype=torch.float32)
+        args0 = _bwd_args(_lib, qq, kq, vq, o, lse, delta, do, *want, accum, causal, sm)
+        _lib.check(lib.qfa_attn_bwd(C.byref(args0), stream), "qfa_attn_bwd")
         dq, dk, dv = (torch.full((B, H, S, D), float("nan"), device="cuda", dtype=torch.bfloat16) for _ in range(3))
         args = _bwd_args(_lib, qq, kq, vq, o, lse, delta, do, dq, dk, dv, None, causal, sm)
         _lib.check(lib.qfa_attn_bwd_static_scratch(C.byref(args), stream), "qfa_attn_bwd_static_scratch")
