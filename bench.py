@@ -251,6 +251,16 @@ def run_ours(args):
         extra["fwd_causal"] = {"ms": c_ms, "TOPS": fwd_ops(B, H, S, S, D, True) / c_ms / 1e9}
         n_ms = time_ms(lambda: qfa.int8_attention_forward(qq, kq, vq, False, sm, torch.bfloat16, o=o, lse=lse))
         extra["fwd_noncausal_kernel"] = {"ms": n_ms, "TOPS": ops_step / n_ms / 1e9}
+        # forward + backward at the headline shape (ops = 3.5 x forward, test_speed.py:114-116)
+        hdo = torch.randn_like(q)
+        for causal in (False, True):
+            ho, hlse = qfa.int8_attention_forward(qq, kq, vq, causal, sm, torch.bfloat16)
+            f_ms = time_ms(lambda: qfa.int8_attention_forward(qq, kq, vq, causal, sm, torch.bfloat16, o=o, lse=lse), reps=5)
+            b_ms = time_ms(lambda: qfa.int8_attention_backward(qq, kq, vq, causal, sm, ho, hlse, hdo), reps=5)
+            fo = fwd_ops(B, H, S, S, D, causal)
+            extra["fwd_bwd_B4H32S4096D128_" + ("causal" if causal else "noncausal")] = {
+                "fwd_ms": f_ms, "bwd_ms": b_ms, "bwd_TOPS": 2.5 * fo / b_ms / 1e9, "TOPS": 3.5 * fo / (f_ms + b_ms) / 1e9}
+        del hdo, ho, hlse
         # training shape: B8 H16 S2048 D64 causal, forward + backward (ops = 3.5 x forward)
         tb, th, ts, td = 8, 16, 2048, 64
         tq, tk, tv = make_inputs(tb, th, ts, td, dev, seed_base=99)

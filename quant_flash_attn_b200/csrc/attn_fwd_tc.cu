@@ -369,6 +369,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     // largest excess over the reference that may be fixed by rescaling P in registers (P must not have
     // overflowed its 16-bit type); beyond that the tile is recomputed from S, which is still intact
     constexpr float kInRegMax = std::is_same<T, __half>::value ? 15.0f : 100.0f;
+    // how far (in powers of two) a tile may exceed the reference before the reference is raised.  P is stored in
+    // T: fp16 keeps P <= 2^8 well inside its range; bf16 has fp32's exponent range and constant relative
+    // precision, so P, l and O may carry a factor up to 2^64 and the rescale path becomes rare even for
+    // heavy-tailed logits
+    constexpr float kGrow = std::is_same<T, __half>::value ? 8.0f : 64.0f;
     float ref[4] = {0.f, 0.f, 0.f, 0.f}, l_run[4] = {0.f, 0.f, 0.f, 0.f};
     const int my_n = n_t[t];
     bool ok = true;
@@ -444,13 +449,13 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         // ---- rare: some row exceeded its reference by more than 2^8
         bool grow = false;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) grow |= emax[k] > 8.0f;
+        for (int k = 0; k < 4; ++k) grow |= emax[k] > kGrow;
         if (__any_sync(0xffffffffu, grow)) {
           float kf[4], factor[4];
           bool redo = false;
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            kf[k] = (emax[k] > 8.0f) ? ceilf(emax[k]) : 0.f;       // whole number: 2^-kf is exact
+            kf[k] = (emax[k] > kGrow) ? ceilf(emax[k]) : 0.f;      // whole number: 2^-kf is exact
             factor[k] = fast_exp2(-kf[k]);
             redo |= emax[k] > kInRegMax;
           }
