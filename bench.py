@@ -2,6 +2,7 @@
 """Benchmark of the quantized-attention hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --profile-case quant|fwd|fwd_causal|bwd     (small fixed case for a profiler capture)
 
 Workload (N=1): INT8 attention forward at B=4 H=32 S=4096 D=128, bf16 inputs ~N(0,1) with 1 % of
 the channels scaled x20, seeded, non-causal.  One step = quantize Q, K, V per token (3 launches of
@@ -338,14 +339,47 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_profile_case(case: str):
+    """A small case of one kernel, launched twice, for a profiler capture: large enough that the operands
+    exceed L2 only for the quantizer (1 Mi tokens); the attention cases are B1 H16 S4096 D128 (a few hundred
+    microseconds per launch, 1.7 waves of CTAs)."""
+    import quant_flash_attn_b200 as qfa
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    if case == "quant":
+        x = torch.randn(8, 32, 4096, 128, device=dev, dtype=torch.bfloat16)
+        for _ in range(2):
+            out = qfa.asymmetric_quant_per_token(x)
+        torch.cuda.synchronize()
+        print("ok", int(out[0].int().sum()))
+        return
+    b, h, s, d = 1, 16, 4096, 128
+    causal = case == "fwd_causal"
+    sm = 1.0 / math.sqrt(d)
+    q, k, v, do = (torch.randn(b, h, s, d, device=dev, dtype=torch.bfloat16) for _ in range(4))
+    qq, kq, vq = qfa.quantize_qkv(q, k, v)
+    reps = 1 if case == "bwd" else 2
+    for _ in range(reps):
+        o, lse = qfa.int8_attention_forward(qq, kq, vq, causal, sm, torch.bfloat16)
+    if case == "bwd":
+        for _ in range(2):
+            dq, dk, dv = qfa.int8_attention_backward(qq, kq, vq, False, sm, o, lse, do)
+        o = dq
+    torch.cuda.synchronize()
+    print("ok", float(o.float().abs().mean()))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--profile-case", default=None, choices=["quant", "fwd", "fwd_causal", "bwd"])
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.profile_case:
+        run_profile_case(args.profile_case)
+    elif args.impl == "reference":
         run_reference_arm(args)
     else:
         run_ours(args)

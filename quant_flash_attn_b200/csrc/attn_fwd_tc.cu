@@ -92,20 +92,20 @@ struct RowConst4 {
   float2 a2[4], A2[4], zq2[4], nref2[4];
 };
 
-// One block of 32 columns for the four rows of a thread.  sA / sB hold the int32 accumulators of rows
+// One block of 16 columns for the four rows of a thread.  sA / sB hold the int32 accumulators of rows
 // (g, g+8) / (g+16, g+24) in the 16x256b fragment layout: element [4n + 2*(row&1) + e] is column
 // 8n + 2q + e.  `meta` points at z_k of column (block start + 2q); -sum(k) and s_k follow at +BN and +2*BN
 // floats, so the three constants of a column pair are loaded once and used for all four rows.
 // lim[k] = first masked column of row k relative to (block start + 2q).  pA / pB receive P packed to
 // 16 bit in the 16x128b store layout (word 2n + (row&1)).
 template <typename T, int BN, bool MASKED, bool MAX_ONLY>
-__device__ __forceinline__ void softmax_block(const uint32_t (&sA)[16], const uint32_t (&sB)[16], const float* meta,
+__device__ __forceinline__ void softmax_block(const uint32_t (&sA)[8], const uint32_t (&sB)[8], const float* meta,
                                               const int (&lim)[4], const RowConst4& rc, float (&emax)[4],
                                               float2 (&lsum2)[4], uint32_t* pA, uint32_t* pB) {
   using H16 = Half16<T>;
   const float2 negM2 = make_float2(-12582912.0f, -12582912.0f);
 #pragma unroll
-  for (int n = 0; n < 4; ++n) {
+  for (int n = 0; n < 2; ++n) {
     const float2 y2 = *reinterpret_cast<const float2*>(meta + 8 * n);
     const float2 z2 = *reinterpret_cast<const float2*>(meta + BN + 8 * n);
     const float2 x2 = *reinterpret_cast<const float2*>(meta + 2 * BN + 8 * n);
@@ -405,22 +405,28 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
         for (int k = 0; k < 4; ++k) lsum2[k] = make_float2(0.f, 0.f);
         uint32_t pA[32], pB[32];                      // P of rows (g, g+8) / (g+16, g+24), 64 packed columns
-        uint32_t sA[16], sB[16];
 
-        // processes the whole tile; MAXONLY computes only the row maxima (first tile)
+        // processes the whole tile in blocks of 16 columns; the tensor-memory load of the next block is in
+        // flight while the current one is computed.  MAXONLY computes only the row maxima (first tile)
         auto run_tile = [&](auto maxonly_tag, auto masked_tag) {
           constexpr bool MAXONLY = decltype(maxonly_tag)::value;
           constexpr bool MASKED = decltype(masked_tag)::value;
+          constexpr int NBLK = C::BN / 16;
+          uint32_t sA[2][8], sB[2][8];
+          tmem_ld_16x256b_x2(tS, sA[0]);
+          tmem_ld_16x256b_x2(tS + kLane16, sB[0]);
 #pragma unroll
-          for (int blk = 0; blk < C::BN / 32; ++blk) {
-            tmem_ld_16x256b_x4(tS + blk * 32, sA);
-            tmem_ld_16x256b_x4(tS + kLane16 + blk * 32, sB);
-            tmem_wait_ld();
+          for (int blk = 0; blk < NBLK; ++blk) {
+            tmem_wait_ld_use(sA[blk & 1], sB[blk & 1]);
+            if (blk + 1 < NBLK) {
+              tmem_ld_16x256b_x2(tS + (blk + 1) * 16, sA[(blk + 1) & 1]);
+              tmem_ld_16x256b_x2(tS + kLane16 + (blk + 1) * 16, sB[(blk + 1) & 1]);
+            }
             int lim_b[4];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) lim_b[k] = lim[k] - blk * 32;
-            softmax_block<T, C::BN, MASKED, MAXONLY>(sA, sB, meta + blk * 32, lim_b, rc, emax, lsum2, pA + blk * 8,
-                                                     pB + blk * 8);
+            for (int k = 0; k < 4; ++k) lim_b[k] = lim[k] - blk * 16;
+            softmax_block<T, C::BN, MASKED, MAXONLY>(sA[blk & 1], sB[blk & 1], meta + blk * 16, lim_b, rc, emax, lsum2,
+                                                     pA + blk * 4, pB + blk * 4);
           }
         };
         auto quad_max = [&]() {

@@ -152,6 +152,25 @@ __device__ __forceinline__ void tmem_ld_16x256b_x4(uint32_t taddr, uint32_t (&r)
 }
 // 16 lanes x 128 bit, 16 repetitions (64 columns): thread (g, q) supplies, for repetition n,
 // r[2n] -> lane g, column 4n+q and r[2n+1] -> lane g+8, column 4n+q.
+// Two 8-column groups (16 columns) of the same fragment layout.
+__device__ __forceinline__ void tmem_ld_16x256b_x2(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+      : "r"(taddr));
+}
+
+// Wait for the outstanding tensor-memory loads; the destination registers of the load that is about to be
+// consumed are passed through as read-write operands so that no use of them can be scheduled above the wait
+// while a younger load (issued after this wait into other registers) is still in flight.
+__device__ __forceinline__ void tmem_wait_ld_use(uint32_t (&a)[8], uint32_t (&b)[8]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(a[0]), "+r"(a[1]), "+r"(a[2]), "+r"(a[3]), "+r"(a[4]), "+r"(a[5]), "+r"(a[6]), "+r"(a[7]),
+                 "+r"(b[0]), "+r"(b[1]), "+r"(b[2]), "+r"(b[3]), "+r"(b[4]), "+r"(b[5]), "+r"(b[6]), "+r"(b[7])
+               :
+               : "memory");
+}
+
 __device__ __forceinline__ void tmem_st_16x128b_x16(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.st.sync.aligned.16x128b.x16.b32 [%0], "
