@@ -10,9 +10,10 @@
 //
 // One CTA owns two 128-row query tiles of one (batch, head) and walks over 128-token K/V tiles.
 // Warp roles: warp 0 = TMA producer (+ per-column constants), warp 1 = MMA issuer, warp 2 = tensor
-// memory allocator, warps 4-7 / 8-11 = softmax of query tile 0 / 1.  A softmax warp reads S in the
-// 16x256b fragment layout (a thread owns 4 rows x 32 columns), so the per-column constants are read
-// from shared memory once per four rows, row max / sum are quad shuffles, and the element-wise math
+// memory allocator, warps 4-11 / 12-19 = softmax of query tile 0 / 1 (two warps per 32-lane quarter of
+// tensor memory, 16 rows each).  A softmax warp reads S in the 16x256b fragment layout (a thread owns
+// 2 rows x 32 columns), so the per-column constants are read from shared memory once per two rows,
+// row max / sum are quad shuffles, and the element-wise math
 // runs on packed f32x2 instructions in a single pass per tile: P is formed against a lazily raised
 // reference instead of the exact running max, and O, l and P are rescaled (by exact powers of two)
 // only when a tile exceeds the reference by more than 2^8.  The two query tiles ping-pong: while
@@ -76,8 +77,10 @@ struct TcCfg {
   static constexpr int NBARS = 1 + 2 * KSTAGES + 2 * VSTAGES + 2 * MSTAGES + 3 * NQT;
   static constexpr int MISC_OFF = BAR_OFF + NBARS * 8;
   static constexpr int SMEM = MISC_OFF + 16 + 1024;      // + slack for 1024-byte alignment of the base
-  static constexpr int SOFTMAX_THREADS = NQT * BM;       // one warp per 32 rows; a thread owns 4 rows x 32 columns
+  static constexpr int SOFTMAX_THREADS = 2 * NQT * BM;   // one warp per 16 rows; a thread owns 2 rows x 32 columns
   static constexpr int THREADS = 128 + SOFTMAX_THREADS;
+  // register budgets after the hand-over between warpgroups (setmaxnreg); see the kernel
+  static constexpr int LAUNCH_REGS = 96, CONTROL_REGS = 56, SOFTMAX_REGS = 104;
   // tensor memory columns
   static constexpr int S_COL = 0;                        // S_t at t*BN (int32), P_t aliases its first BN/2 columns
   static constexpr int O_COL = NQT * BN;                 // O_t at O_COL + t*D (fp32)
@@ -85,23 +88,22 @@ struct TcCfg {
   static constexpr uint32_t QK_SWIZZLE_ROWS_BYTES = 8 * D;    // 8 rows of D bytes per swizzle atom
 };
 
-// Per-row constants of a softmax thread (each thread owns four rows).  With a = s_q*sm_scale*log2(e):
+// Per-row constants of a softmax thread (each thread owns two rows).  With a = s_q*sm_scale*log2(e):
 //   logit*log2e - ref = a * s_k * (S + A*z_k - z_q*sum(k)) - ref,    A = D*z_q - sum(q)
 // Every value is kept as a pair of equal halves because the math runs on packed f32x2 instructions.
-struct RowConst4 {
-  float2 a2[4], A2[4], zq2[4], nref2[4];
+struct RowConst2 {
+  float2 a2[2], A2[2], zq2[2], nref2[2];
 };
 
-// One block of 16 columns for the four rows of a thread.  sA / sB hold the int32 accumulators of rows
-// (g, g+8) / (g+16, g+24) in the 16x256b fragment layout: element [4n + 2*(row&1) + e] is column
-// 8n + 2q + e.  `meta` points at z_k of column (block start + 2q); -sum(k) and s_k follow at +BN and +2*BN
-// floats, so the three constants of a column pair are loaded once and used for all four rows.
-// lim[k] = first masked column of row k relative to (block start + 2q).  pA / pB receive P packed to
-// 16 bit in the 16x128b store layout (word 2n + (row&1)).
+// One block of 16 columns for the two rows (g, g+8) of a thread.  s holds the int32 accumulators in the
+// 16x256b fragment layout: element [4n + 2*row + e] is column 8n + 2q + e.  `meta` points at z_k of column
+// (block start + 2q); -sum(k) and s_k follow at +BN and +2*BN floats, so the three constants of a column
+// pair are loaded once and used for both rows.  lim[k] = first masked column of row k relative to
+// (block start + 2q).  pw receives P packed to 16 bit in the 16x128b store layout (word 2n + row).
 template <typename T, int BN, bool MASKED, bool MAX_ONLY>
-__device__ __forceinline__ void softmax_block(const uint32_t (&sA)[8], const uint32_t (&sB)[8], const float* meta,
-                                              const int (&lim)[4], const RowConst4& rc, float (&emax)[4],
-                                              float2 (&lsum2)[4], uint32_t* pA, uint32_t* pB) {
+__device__ __forceinline__ void softmax_block(const uint32_t (&s)[8], const float* meta, const int (&lim)[2],
+                                              const RowConst2& rc, float (&emax)[2], float2 (&lsum2)[2],
+                                              uint32_t* pw) {
   using H16 = Half16<T>;
   const float2 negM2 = make_float2(-12582912.0f, -12582912.0f);
 #pragma unroll
@@ -110,9 +112,8 @@ __device__ __forceinline__ void softmax_block(const uint32_t (&sA)[8], const uin
     const float2 z2 = *reinterpret_cast<const float2*>(meta + BN + 8 * n);
     const float2 x2 = *reinterpret_cast<const float2*>(meta + 2 * BN + 8 * n);
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const uint32_t s0 = (k < 2) ? sA[4 * n + 2 * (k & 1)] : sB[4 * n + 2 * (k & 1)];
-      const uint32_t s1 = (k < 2) ? sA[4 * n + 2 * (k & 1) + 1] : sB[4 * n + 2 * (k & 1) + 1];
+    for (int k = 0; k < 2; ++k) {
+      const uint32_t s0 = s[4 * n + 2 * k], s1 = s[4 * n + 2 * k + 1];
       // int32 -> fp32 without the conversion pipe: |S| <= 128*128*D < 2^22, so the bit pattern of 1.5*2^23
       // plus S is the float 1.5*2^23 + S.  Everything up to the multiply by s_k is exact integer arithmetic
       // in fp32 (|S + z_k*A - sum(k)*z_q| <= 255*255*D < 2^24): with large scales one integer step is several
@@ -131,15 +132,14 @@ __device__ __forceinline__ void softmax_block(const uint32_t (&sA)[8], const uin
       if (!MAX_ONLY) {
         const float p0 = fast_exp2(v.x), p1 = fast_exp2(v.y);
         lsum2[k] = __fadd2_rn(lsum2[k], make_float2(p0, p1));
-        const uint32_t w = H16::pack(p0, p1);       // P rounded to 16 bit (quant_flash_attn.py:75)
-        if (k < 2) pA[2 * n + (k & 1)] = w; else pB[2 * n + (k & 1)] = w;
+        pw[2 * n + k] = H16::pack(p0, p1);            // P rounded to 16 bit (quant_flash_attn.py:75)
       }
     }
   }
 }
 
 template <typename T, int D>
-__global__ void __launch_bounds__(384, 1)
+__global__ void __launch_bounds__(TcCfg<D>::THREADS, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const TcFwdParams p) {
   using C = TcCfg<D>;
@@ -185,7 +185,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     for (int i = 0; i < C::MSTAGES; ++i) { mbar_init(BAR(B_MFULL + i), 32); mbar_init(BAR(B_MEMPTY + i), C::SOFTMAX_THREADS); }
     for (int t = 0; t < C::NQT; ++t) {
       mbar_init(BAR(B_SFULL + t), 1);
-      mbar_init(BAR(B_PFULL + t), C::BM);
+      mbar_init(BAR(B_PFULL + t), 2 * C::BM);
       mbar_init(BAR(B_ODONE + t), 1);
     }
     fence_barrier_init();
@@ -199,14 +199,15 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
 
-  // the softmax warpgroups hold a whole 128-column row per thread: move registers to them
   if (warp < 4) {
-  // control warpgroup: give registers away (the softmax warpgroups hold a whole row per thread)
-  // Register hand-over between warpgroups.  setmaxnreg.inc BLOCKS until the CTA's pool (threads x registers
-  // the kernel was launched with) has enough free registers, so the two budgets must fit that pool or the
-  // softmax warps would wait forever.
-  static_assert(128 * 96 + C::SOFTMAX_THREADS * 192 <= C::THREADS * 168, "setmaxnreg budgets exceed the CTA's registers");
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
+  // Register hand-over between warpgroups: the control warps give registers to the softmax warps.
+  // setmaxnreg.inc BLOCKS until the CTA's pool (threads x registers the kernel was launched with) has enough
+  // free registers, so the two budgets must fit that pool or the softmax warps would wait forever; the host
+  // side refuses to launch if the compiled kernel has fewer registers per thread than LAUNCH_REGS.
+  static_assert(128 * C::CONTROL_REGS + C::SOFTMAX_THREADS * C::SOFTMAX_REGS <= C::THREADS * C::LAUNCH_REGS,
+                "setmaxnreg budgets exceed the CTA's registers");
+  static_assert(C::CONTROL_REGS == 56 && C::SOFTMAX_REGS == 104, "keep the asm immediates below in step");
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
   if (warp == 0) {
     // ================================================================ producer
     if (lane == 0) {
@@ -333,26 +334,27 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
   }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 192;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
     // ================================================================ softmax
-    // One warp per 32 rows of a query tile.  S is read in the 16x256b fragment layout: thread (g, q) of the
-    // warp owns rows g, g+8, g+16, g+24 of its lane quarter and columns 8n+2q, 8n+2q+1, so the three
-    // per-column constants are fetched from shared memory once per four rows and row reductions are
-    // two quad shuffles.  P = exp2(logit - ref) is formed in the same pass that finds the tile max, against a
-    // reference that is only raised (by a whole number: exact power-of-two rescale of O, l and P) when a
-    // tile exceeds it by more than 2^8; after the first tiles that almost never happens.
-    const int t = (warp - 4) >> 2;                 // query tile of this warpgroup
+    // One warp per 16 rows of a query tile.  S is read in the 16x256b fragment layout: thread (g, q) of the
+    // warp owns rows g, g+8 of its 16-lane half and columns 8n+2q, 8n+2q+1, so the three per-column constants
+    // are fetched from shared memory once per two rows and row reductions are two quad shuffles.
+    // P = exp2(logit - ref) is formed in the same pass that finds the tile max, against a reference that is
+    // only raised (by a whole number: exact power-of-two rescale of O, l and P) when a tile exceeds it by
+    // more than kGrow; after the first tiles that almost never happens.
+    const int sw = warp - 4;
+    const int t = sw >> 3;                         // query tile of this warpgroup
+    const int hh = (sw >> 2) & 1;                  // which 16 lanes of the quarter
     const int wq = warp & 3;                       // tensor-memory lane quarter this warp may access
     const int g = lane >> 2, q = lane & 3;
-    const uint32_t quarter = static_cast<uint32_t>(wq * 32) << 16;
-    const uint32_t tS = tmem + quarter + C::S_COL + t * C::BN;
-    const uint32_t tO = tmem + quarter + C::O_COL + t * D;
-    constexpr uint32_t kLane16 = 16u << 16;
-    int rowk[4];
-    RowConst4 rc;
+    const uint32_t lanes = static_cast<uint32_t>(wq * 32 + hh * 16) << 16;
+    const uint32_t tS = tmem + lanes + C::S_COL + t * C::BN;
+    const uint32_t tO = tmem + lanes + C::O_COL + t * D;
+    int rowk[2];
+    RowConst2 rc;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      rowk[k] = m0 + t * C::BM + wq * 32 + g + 8 * k;
+    for (int k = 0; k < 2; ++k) {
+      rowk[k] = m0 + t * C::BM + wq * 32 + hh * 16 + g + 8 * k;
       float A = 0.f, zq = 0.f, a = 0.f;
       if (rowk[k] < p.Sq) {
         const int64_t tk = static_cast<int64_t>(bh) * p.Sq + rowk[k];
@@ -374,13 +376,13 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     // precision, so P, l and O may carry a factor up to 2^64 and the rescale path becomes rare even for
     // heavy-tailed logits
     constexpr float kGrow = std::is_same<T, __half>::value ? 8.0f : 64.0f;
-    float ref[4] = {0.f, 0.f, 0.f, 0.f}, l_run[4] = {0.f, 0.f, 0.f, 0.f};
+    float ref[2] = {0.f, 0.f}, l_run[2] = {0.f, 0.f};
     const int my_n = n_t[t];
     bool ok = true;
     for (int j = 0; j < n_max && ok; ++j) {
       const int ms = j % C::MSTAGES;
       if (j < my_n) {
-        const bool tr = (wq == 0 && lane == 0);
+        const bool tr = (sw == 8 * t && lane == 0);
         if (tr) QFA_TRACE(0, j, t, 0);
         ok = mbar_wait(BAR(B_MFULL + ms), (j / C::MSTAGES) & 1, abort_flag, p.epoch);
         if (ok) ok = mbar_wait(BAR(B_SFULL + t), j & 1, abort_flag, p.epoch);
@@ -390,21 +392,21 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (tr) QFA_TRACE(0, j, t, 1);
         const float* meta = reinterpret_cast<const float*>(smem + C::M_OFF + ms * C::M_BYTES) + 2 * q;
         const int n0 = j * C::BN;
-        int lim[4];                                   // first masked column of each row, relative to 2q
+        int lim[2];                                   // first masked column of each row, relative to 2q
         bool any_masked = false;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
+        for (int k = 0; k < 2; ++k) {
           int cl = p.Skv - n0;
           if (p.causal) cl = min(cl, rowk[k] + 1 - n0);
           any_masked |= cl < C::BN;
           lim[k] = cl - 2 * q;
         }
         const bool masked = __any_sync(0xffffffffu, any_masked);
-        float emax[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-        float2 lsum2[4];
+        float emax[2] = {-INFINITY, -INFINITY};
+        float2 lsum2[2];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) lsum2[k] = make_float2(0.f, 0.f);
-        uint32_t pA[32], pB[32];                      // P of rows (g, g+8) / (g+16, g+24), 64 packed columns
+        for (int k = 0; k < 2; ++k) lsum2[k] = make_float2(0.f, 0.f);
+        uint32_t pw[32];                              // P of rows (g, g+8), 64 packed columns
 
         // processes the whole tile in blocks of 16 columns; the tensor-memory load of the next block is in
         // flight while the current one is computed.  MAXONLY computes only the row maxima (first tile)
@@ -412,26 +414,22 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           constexpr bool MAXONLY = decltype(maxonly_tag)::value;
           constexpr bool MASKED = decltype(masked_tag)::value;
           constexpr int NBLK = C::BN / 16;
-          uint32_t sA[2][8], sB[2][8];
-          tmem_ld_16x256b_x2(tS, sA[0]);
-          tmem_ld_16x256b_x2(tS + kLane16, sB[0]);
+          uint32_t sreg[2][8];
+          tmem_ld_16x256b_x2(tS, sreg[0]);
 #pragma unroll
           for (int blk = 0; blk < NBLK; ++blk) {
-            tmem_wait_ld_use(sA[blk & 1], sB[blk & 1]);
-            if (blk + 1 < NBLK) {
-              tmem_ld_16x256b_x2(tS + (blk + 1) * 16, sA[(blk + 1) & 1]);
-              tmem_ld_16x256b_x2(tS + kLane16 + (blk + 1) * 16, sB[(blk + 1) & 1]);
-            }
-            int lim_b[4];
+            tmem_wait_ld_use(sreg[blk & 1]);
+            if (blk + 1 < NBLK) tmem_ld_16x256b_x2(tS + (blk + 1) * 16, sreg[(blk + 1) & 1]);
+            int lim_b[2];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) lim_b[k] = lim[k] - blk * 16;
-            softmax_block<T, C::BN, MASKED, MAXONLY>(sA[blk & 1], sB[blk & 1], meta + blk * 16, lim_b, rc, emax, lsum2,
-                                                     pA + blk * 4, pB + blk * 4);
+            for (int k = 0; k < 2; ++k) lim_b[k] = lim[k] - blk * 16;
+            softmax_block<T, C::BN, MASKED, MAXONLY>(sreg[blk & 1], meta + blk * 16, lim_b, rc, emax, lsum2,
+                                                     pw + blk * 4);
           }
         };
         auto quad_max = [&]() {
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
+          for (int k = 0; k < 2; ++k) {
             emax[k] = fmaxf(emax[k], __shfl_xor_sync(0xffffffffu, emax[k], 1));
             emax[k] = fmaxf(emax[k], __shfl_xor_sync(0xffffffffu, emax[k], 2));
           }
@@ -442,7 +440,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           if (masked) run_tile(std::true_type{}, std::true_type{}); else run_tile(std::true_type{}, std::false_type{});
           quad_max();
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
+          for (int k = 0; k < 2; ++k) {
             ref[k] = (emax[k] == -INFINITY) ? 0.f : emax[k];
             rc.nref2[k] = make_float2(-ref[k], -ref[k]);
             emax[k] = -INFINITY;
@@ -452,15 +450,13 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (tr) QFA_TRACE(0, j, t, 3);
         quad_max();
 
-        // ---- rare: some row exceeded its reference by more than 2^8
-        bool grow = false;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) grow |= emax[k] > kGrow;
+        // ---- rare: some row exceeded its reference by more than 2^kGrow
+        const bool grow = emax[0] > kGrow || emax[1] > kGrow;
         if (__any_sync(0xffffffffu, grow)) {
-          float kf[4], factor[4];
+          float kf[2], factor[2];
           bool redo = false;
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
+          for (int k = 0; k < 2; ++k) {
             kf[k] = (emax[k] > kGrow) ? ceilf(emax[k]) : 0.f;      // whole number: 2^-kf is exact
             factor[k] = fast_exp2(-kf[k]);
             redo |= emax[k] > kInRegMax;
@@ -470,26 +466,22 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after_sync();
-            // O is rescaled in the plain row-per-thread layout: fetch the factor of row `lane`
-            float f_row = 1.f;
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const float f = __shfl_sync(0xffffffffu, factor[k], 4 * (lane & 7));
-              if ((lane >> 3) == k) f_row = f;
-            }
+            // O of this warp's 16 rows, in the same fragment layout (the other 16 lanes of the quarter belong
+            // to the partner warp, which may be rescaling them at the same time)
 #pragma unroll 1
-            for (int c = 0; c < D / 8; ++c) {
-              uint32_t oreg[8];
-              tmem_ld8(tO + c * 8, oreg);
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t oreg[16];
+              tmem_ld_16x256b_x4(tO + c * 32, oreg);
               tmem_wait_ld();
 #pragma unroll
-              for (int i = 0; i < 8; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * f_row);
-              tmem_st8(tO + c * 8, oreg);
+              for (int i = 0; i < 16; ++i)
+                oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * factor[(i >> 1) & 1]);
+              tmem_st_16x256b_x4(tO + c * 32, oreg);
             }
             tmem_wait_st();
           }
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
+          for (int k = 0; k < 2; ++k) {
             l_run[k] *= factor[k];
             ref[k] += kf[k];
             rc.nref2[k] = make_float2(-ref[k], -ref[k]);
@@ -497,30 +489,26 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           if (__any_sync(0xffffffffu, redo)) {
             // P may have overflowed its 16-bit type: recompute the tile against the new reference
 #pragma unroll
-            for (int k = 0; k < 4; ++k) { lsum2[k] = make_float2(0.f, 0.f); emax[k] = -INFINITY; }
+            for (int k = 0; k < 2; ++k) { lsum2[k] = make_float2(0.f, 0.f); emax[k] = -INFINITY; }
             run_tile(std::false_type{}, std::true_type{});
           } else {
             // exact power-of-two rescale of the P already packed in registers and of its row sums
-            uint32_t f2[4];
+            uint32_t f2[2];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) { f2[k] = H16::pack(factor[k], factor[k]); lsum2[k].x *= factor[k]; lsum2[k].y *= factor[k]; }
+            for (int k = 0; k < 2; ++k) { f2[k] = H16::pack(factor[k], factor[k]); lsum2[k].x *= factor[k]; lsum2[k].y *= factor[k]; }
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-              typename H16::T2 va = __hmul2(*reinterpret_cast<typename H16::T2*>(&pA[i]),
+              typename H16::T2 va = __hmul2(*reinterpret_cast<typename H16::T2*>(&pw[i]),
                                             *reinterpret_cast<const typename H16::T2*>(&f2[i & 1]));
-              typename H16::T2 vb = __hmul2(*reinterpret_cast<typename H16::T2*>(&pB[i]),
-                                            *reinterpret_cast<const typename H16::T2*>(&f2[2 + (i & 1)]));
-              pA[i] = *reinterpret_cast<uint32_t*>(&va);
-              pB[i] = *reinterpret_cast<uint32_t*>(&vb);
+              pw[i] = *reinterpret_cast<uint32_t*>(&va);
             }
           }
         }
         mbar_arrive(BAR(B_MEMPTY + ms));
 #pragma unroll
-        for (int k = 0; k < 4; ++k) l_run[k] += lsum2[k].x + lsum2[k].y;
+        for (int k = 0; k < 2; ++k) l_run[k] += lsum2[k].x + lsum2[k].y;
         if (tr) QFA_TRACE(0, j, t, 5);
-        tmem_st_16x128b_x16(tS, pA);
-        tmem_st_16x128b_x16(tS + kLane16, pB);
+        tmem_st_16x128b_x16(tS, pw);
         if (tr) QFA_TRACE(0, j, t, 6);
         tmem_wait_st();
         tc_fence_before_sync();
@@ -541,35 +529,30 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (ok) {
         tc_fence_after_sync();
         // row sums: the four threads of a quad hold partial sums of the same rows
-        float inv_row = 0.f;
+        float inv[2];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
+        for (int k = 0; k < 2; ++k) {
           float l = l_run[k];
           l += __shfl_xor_sync(0xffffffffu, l, 1);
           l += __shfl_xor_sync(0xffffffffu, l, 2);
           if (q == 0 && rowk[k] < p.Sq)
             p.lse[static_cast<int64_t>(bh) * p.lse_stride + rowk[k]] = (ref[k] + log2f(l)) * kLn2;
-          const float inv = l > 0.f ? 1.f / l : 0.f;
-          // O is read in the plain row-per-thread layout: hand row `lane` its 1/l
-          const float v = __shfl_sync(0xffffffffu, inv, 4 * (lane & 7));
-          if ((lane >> 3) == k) inv_row = v;
+          inv[k] = l > 0.f ? 1.f / l : 0.f;
         }
-        const int row = m0 + t * C::BM + wq * 32 + lane;
-        T* orow = static_cast<T*>(p.o) + b * p.o_stride[0] + h * p.o_stride[1] + static_cast<int64_t>(row) * p.o_stride[2];
+        T* obase = static_cast<T*>(p.o) + b * p.o_stride[0] + h * p.o_stride[1];
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
-          uint32_t oreg[32];
-          tmem_ld32(tO + c * 32, oreg);
+          uint32_t oreg[16];
+          tmem_ld_16x256b_x4(tO + c * 32, oreg);
           tmem_wait_ld();
-          if (row < p.Sq) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              uint4 v;
-              v.x = H16::pack(__uint_as_float(oreg[i]) * inv_row, __uint_as_float(oreg[i + 1]) * inv_row);
-              v.y = H16::pack(__uint_as_float(oreg[i + 2]) * inv_row, __uint_as_float(oreg[i + 3]) * inv_row);
-              v.z = H16::pack(__uint_as_float(oreg[i + 4]) * inv_row, __uint_as_float(oreg[i + 5]) * inv_row);
-              v.w = H16::pack(__uint_as_float(oreg[i + 6]) * inv_row, __uint_as_float(oreg[i + 7]) * inv_row);
-              *reinterpret_cast<uint4*>(orow + c * 32 + i) = v;
+          for (int k = 0; k < 2; ++k) {
+            if (rowk[k] < p.Sq) {
+              T* orow = obase + static_cast<int64_t>(rowk[k]) * p.o_stride[2] + c * 32 + 2 * q;
+#pragma unroll
+              for (int n = 0; n < 4; ++n)
+                *reinterpret_cast<uint32_t*>(orow + 8 * n) =
+                    H16::pack(__uint_as_float(oreg[4 * n + 2 * k]) * inv[k], __uint_as_float(oreg[4 * n + 2 * k + 1]) * inv[k]);
             }
           }
         }
@@ -620,6 +603,10 @@ static int launch_tc(const QfaFwdArgs& a, cudaStream_t stream) {
   QFA_CUDA_TRY(cudaGetDevice(&devid));
   if (devid < 64 && !attr_done[devid]) {
     QFA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+    // the register hand-over inside the kernel assumes this many registers per thread at launch
+    cudaFuncAttributes fa;
+    QFA_CUDA_TRY(cudaFuncGetAttributes(&fa, kern));
+    if (fa.numRegs < C::LAUNCH_REGS) return cuda_fail(cudaErrorLaunchOutOfResources, "forward kernel register pool");
     attr_done[devid] = true;
   }
   const int64_t n_ctas = ((a.Sq + C::NQT * C::BM - 1) / (C::NQT * C::BM)) * a.B * a.H;
