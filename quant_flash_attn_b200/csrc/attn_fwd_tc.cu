@@ -96,21 +96,21 @@ struct RowConst2 {
 };
 
 // One block of 16 columns for the two rows (g, g+8) of a thread.  s holds the int32 accumulators in the
-// 16x256b fragment layout: element [4n + 2*row + e] is column 8n + 2q + e.  `meta` points at z_k of column
-// (block start + 2q); -sum(k) and s_k follow at +BN and +2*BN floats, so the three constants of a column
-// pair are loaded once and used for both rows.  lim[k] = first masked column of row k relative to
+// 16x256b fragment layout: element [4n + 2*row + e] is column 8n + 2q + e.  `meta` points at this thread's three
+// 16-byte words of the block: z_k, -sum(k), s_k of its four columns, loaded once and used for both rows.  lim[k] = first masked column of row k relative to
 // (block start + 2q).  pw receives P packed to 16 bit in the 16x128b store layout (word 2n + row).
 template <typename T, int BN, bool MASKED, bool MAX_ONLY>
-__device__ __forceinline__ void softmax_block(const uint32_t (&s)[8], const float* meta, const int (&lim)[2],
+__device__ __forceinline__ void softmax_block(const uint32_t (&s)[8], const float4* meta, const int (&lim)[2],
                                               const RowConst2& rc, float (&emax)[2], float2 (&lsum2)[2],
                                               uint32_t* pw) {
   using H16 = Half16<T>;
   const float2 negM2 = make_float2(-12582912.0f, -12582912.0f);
+  const float4 y4 = meta[0], z4 = meta[1], x4 = meta[2];
 #pragma unroll
   for (int n = 0; n < 2; ++n) {
-    const float2 y2 = *reinterpret_cast<const float2*>(meta + 8 * n);
-    const float2 z2 = *reinterpret_cast<const float2*>(meta + BN + 8 * n);
-    const float2 x2 = *reinterpret_cast<const float2*>(meta + 2 * BN + 8 * n);
+    const float2 y2 = n ? make_float2(y4.z, y4.w) : make_float2(y4.x, y4.y);
+    const float2 z2 = n ? make_float2(z4.z, z4.w) : make_float2(z4.x, z4.y);
+    const float2 x2 = n ? make_float2(x4.z, x4.w) : make_float2(x4.x, x4.y);
 #pragma unroll
     for (int k = 0; k < 2; ++k) {
       const uint32_t s0 = s[4 * n + 2 * k], s1 = s[4 * n + 2 * k + 1];
@@ -246,9 +246,13 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           zk = static_cast<float>(p.k_zp[tok_k0 + n]);
           nks = -static_cast<float>(p.k_sum[tok_k0 + n]);
         }
-        meta[col] = zk;
-        meta[C::BN + col] = nks;
-        meta[2 * C::BN + col] = sk;
+        // layout for the softmax threads: thread q of a quad owns columns 8n+2q, 8n+2q+1; the constants of two
+        // column groups (n even, n odd) are packed into three 16-byte words {z_k}, {-sum(k)}, {s_k}
+        const int n8 = col >> 3, qq = (col >> 1) & 3, e = col & 1;
+        float* dst = meta + (((n8 >> 1) * 4 + qq) * 3) * 4 + (n8 & 1) * 2 + e;
+        dst[0] = zk;
+        dst[4] = nks;
+        dst[8] = sk;
       }
       mbar_arrive(BAR(B_MFULL + ms));
       // V tile (D/64 panels of 128 bytes x BN rows)
@@ -390,7 +394,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (!ok) break;
         tc_fence_after_sync();
         if (tr) QFA_TRACE(0, j, t, 1);
-        const float* meta = reinterpret_cast<const float*>(smem + C::M_OFF + ms * C::M_BYTES) + 2 * q;
+        const float4* meta = reinterpret_cast<const float4*>(smem + C::M_OFF + ms * C::M_BYTES) + 3 * q;
         const int n0 = j * C::BN;
         int lim[2];                                   // first masked column of each row, relative to 2q
         bool any_masked = false;
@@ -423,7 +427,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             int lim_b[2];
 #pragma unroll
             for (int k = 0; k < 2; ++k) lim_b[k] = lim[k] - blk * 16;
-            softmax_block<T, C::BN, MASKED, MAXONLY>(sreg[blk & 1], meta + blk * 16, lim_b, rc, emax, lsum2,
+            softmax_block<T, C::BN, MASKED, MAXONLY>(sreg[blk & 1], meta + blk * 12, lim_b, rc, emax, lsum2,
                                                      pw + blk * 4);
           }
         };
