@@ -182,10 +182,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     mbar_init(BAR(B_QFULL), 1);
     for (int i = 0; i < C::KSTAGES; ++i) { mbar_init(BAR(B_KFULL + i), 1); mbar_init(BAR(B_KEMPTY + i), 1); }
     for (int i = 0; i < C::VSTAGES; ++i) { mbar_init(BAR(B_VFULL + i), 1); mbar_init(BAR(B_VEMPTY + i), 1); }
-    for (int i = 0; i < C::MSTAGES; ++i) { mbar_init(BAR(B_MFULL + i), 32); mbar_init(BAR(B_MEMPTY + i), C::SOFTMAX_THREADS); }
+    for (int i = 0; i < C::MSTAGES; ++i) { mbar_init(BAR(B_MFULL + i), 1); mbar_init(BAR(B_MEMPTY + i), C::SOFTMAX_THREADS / 32); }
     for (int t = 0; t < C::NQT; ++t) {
       mbar_init(BAR(B_SFULL + t), 1);
-      mbar_init(BAR(B_PFULL + t), 2 * C::BM);
+      mbar_init(BAR(B_PFULL + t), C::SOFTMAX_THREADS / 64);   // one arrival per softmax warp of the tile
       mbar_init(BAR(B_ODONE + t), 1);
     }
     fence_barrier_init();
@@ -254,7 +254,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         dst[4] = nks;
         dst[8] = sk;
       }
-      mbar_arrive(BAR(B_MFULL + ms));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(BAR(B_MFULL + ms));
       // V tile (D/64 panels of 128 bytes x BN rows)
       ok = mbar_wait(BAR(B_VEMPTY + vs), ((j / C::VSTAGES) & 1) ^ 1, abort_flag, p.epoch);
       ok = __all_sync(0xffffffffu, ok);
@@ -508,7 +509,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             }
           }
         }
-        mbar_arrive(BAR(B_MEMPTY + ms));
+        // one arrival per warp (the warp's reads of the constants are ordered before it by __syncwarp)
+        __syncwarp();
+        if (lane == 0) mbar_arrive(BAR(B_MEMPTY + ms));
 #pragma unroll
         for (int k = 0; k < 2; ++k) l_run[k] += lsum2[k].x + lsum2[k].y;
         if (tr) QFA_TRACE(0, j, t, 5);
@@ -516,14 +519,15 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (tr) QFA_TRACE(0, j, t, 6);
         tmem_wait_st();
         tc_fence_before_sync();
-        mbar_arrive(BAR(B_PFULL + t));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(BAR(B_PFULL + t));
         if (tr) QFA_TRACE(0, j, t, 7);
       } else {
         // this query tile is done (causal): keep the per-column ring moving for the other tile
         ok = mbar_wait(BAR(B_MFULL + ms), (j / C::MSTAGES) & 1, abort_flag, p.epoch);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        mbar_arrive(BAR(B_MEMPTY + ms));
+        if (lane == 0) mbar_arrive(BAR(B_MEMPTY + ms));
       }
     }
     // ---------------- epilogue: O / l -> 16 bit, LSE = (ref + log2 l) ln 2
