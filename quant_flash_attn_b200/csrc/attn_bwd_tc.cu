@@ -17,9 +17,15 @@
 // recomputed P matches the saved LSE; Q^, K^, V^ are the dequantized 16-bit operands (straight-through
 // gradients).  Tensor memory: T1 | T2 | acc1 | acc2 = 128 + 128 + D + D columns; P / dS are written back as
 // packed 16-bit into the first halves of T1 / T2.
-// Warp roles as in the forward: producer, MMA issuer, tensor-memory allocator, four softmax warps reading in the
-// 16x256b fragment layout (a thread owns 4 rows x 32 columns; the five per-column constants are loaded once per
-// four rows).  All waits are time-bounded.
+// Warp roles: producer (TMA + per-column constants), MMA issuer, tensor-memory allocator, sixteen softmax
+// warps.  The element-wise stage has no row reductions (LSE and delta are inputs), so all sixteen warps share the
+// one tile: a warp owns 16 rows x 64 columns and walks them in blocks of 16 columns, reading in the 16x256b
+// fragment layout (a thread owns 2 rows x 4 columns of a block; the five per-column constants come in as 16-byte
+// shared loads), with the next block's tensor-memory loads in flight while the current block is computed.
+// P / dS of a block go back to tensor memory at once and the block is handed to the MMA issuer through its own
+// mbarrier, so the accumulating MMAs of a 16-column k-step start while the later blocks are still being
+// computed; only the last k-step and the next step's T1 / T2 remain on the critical path.  All waits are
+// time-bounded.
 #include <atomic>
 #include <type_traits>
 
@@ -60,45 +66,52 @@ struct BwdTcCfg {
   static constexpr int ST_BYTES = C_BYTES + 2 * H_BYTES;
   static constexpr int M_OFF = ST_OFF + STAGES * ST_BYTES;
   static constexpr int BAR_OFF = M_OFF + STAGES * M_BYTES;
-  static constexpr int NBARS = 1 + 3 * STAGES + 4;
+  static constexpr int KSTEPS = BN / 16;               // 16-column blocks = k-steps of the accumulating MMAs
+  static constexpr int NBARS = 1 + 3 * STAGES + 3 + KSTEPS;
   static constexpr int MISC_OFF = BAR_OFF + NBARS * 8;
   static constexpr int SMEM = MISC_OFF + 16 + 1024;
-  static constexpr int THREADS = 256;
+  static constexpr int SOFTMAX_WARPS = 16;
+  static constexpr int THREADS = 128 + SOFTMAX_WARPS * 32;
+  // register budgets after the hand-over between warpgroups (setmaxnreg); see the kernel
+  static constexpr int LAUNCH_REGS = 96, CONTROL_REGS = 56, SOFTMAX_REGS = 104;
   static constexpr int T1_COL = 0, T2_COL = 128, ACC1_COL = 256, ACC2_COL = 256 + D;
   static constexpr int TMEM_COLS = 512;
+  // P / dS (16-bit, two per 32-bit column) of column half c overwrite the first 32 columns of that half of
+  // T1 / T2, so warps that share rows never write columns another warp still has to read: k-step kk of the
+  // accumulating MMAs reads its left operand at this column offset
+  __host__ __device__ static constexpr int p_col(int kk) { return (kk / 4) * 64 + (kk % 4) * 8; }
   static_assert(SMEM <= 232448, "shared memory budget");
 };
 
-struct BwdRow4 {
-  float2 a2[4], A2[4], z2[4], nlse2[4], ndelta2[4];
+struct BwdRow2 {
+  float2 a2[2], A2[2], z2[2], nlse2[2], ndelta2[2];
 };
 
-// One block of 32 columns for the four rows of a thread: T1 fragments (int32 logits) + T2 fragments (fp32 dP)
-// -> P and dS packed to 16 bit in the 16x128b store layout.  KV_PASS: LSE / delta belong to the columns
-// (queries) and the causal mask hides columns BELOW the row; otherwise they belong to the rows and the mask
-// hides columns ABOVE the row.
+// One block of 16 columns for the two rows (g, g+8) of a thread: T1 fragments (int32 logits) + T2 fragments
+// (fp32 dP) -> P and dS packed to 16 bit in the 16x128b store layout (word 2n + row).  `meta` points at this
+// thread's five 16-byte words of the block (z, -sum, s, -lse*log2e, -delta of its four columns).  KV_PASS: LSE /
+// delta belong to the columns (queries) and the causal mask hides columns BELOW the row; otherwise they belong
+// to the rows and the mask hides columns ABOVE the row.  Visible columns of row k: lo[k] <= 8n + e < hi[k].
 template <typename T, bool KV_PASS, bool MASKED>
-__device__ __forceinline__ void bwd_block(const uint32_t (&sA)[16], const uint32_t (&sB)[16], const uint32_t (&dA)[16],
-                                          const uint32_t (&dB)[16], const float* meta, const int (&lo)[4],
-                                          const int (&hi)[4], const BwdRow4& rc, uint32_t* pA, uint32_t* pB,
-                                          uint32_t* gA, uint32_t* gB) {
+__device__ __forceinline__ void bwd_block(const uint32_t (&s)[8], const uint32_t (&d)[8], const float4* meta,
+                                          const int (&lo)[2], const int (&hi)[2], const BwdRow2& rc, uint32_t (&pw)[4],
+                                          uint32_t (&gw)[4]) {
   using H16 = Half16<T>;
   const float2 negM2 = make_float2(-12582912.0f, -12582912.0f);
+  const float4 z4 = meta[0], n4 = meta[1], s4 = meta[2];
+  float4 l4 = make_float4(0.f, 0.f, 0.f, 0.f), d4 = l4;
+  if (KV_PASS) { l4 = meta[3]; d4 = meta[4]; }
 #pragma unroll
-  for (int n = 0; n < 4; ++n) {
-    const float2 z2 = *reinterpret_cast<const float2*>(meta + 8 * n);
-    const float2 n2 = *reinterpret_cast<const float2*>(meta + 128 + 8 * n);
-    const float2 s2 = *reinterpret_cast<const float2*>(meta + 256 + 8 * n);
-    float2 l2 = make_float2(0.f, 0.f), d2 = make_float2(0.f, 0.f);
-    if (KV_PASS) {
-      l2 = *reinterpret_cast<const float2*>(meta + 384 + 8 * n);
-      d2 = *reinterpret_cast<const float2*>(meta + 512 + 8 * n);
-    }
+  for (int n = 0; n < 2; ++n) {
+    const float2 z2 = n ? make_float2(z4.z, z4.w) : make_float2(z4.x, z4.y);
+    const float2 n2 = n ? make_float2(n4.z, n4.w) : make_float2(n4.x, n4.y);
+    const float2 s2 = n ? make_float2(s4.z, s4.w) : make_float2(s4.x, s4.y);
+    const float2 l2 = n ? make_float2(l4.z, l4.w) : make_float2(l4.x, l4.y);
+    const float2 d2 = n ? make_float2(d4.z, d4.w) : make_float2(d4.x, d4.y);
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const int i0 = 4 * n + 2 * (k & 1);
-      const uint32_t s0 = (k < 2) ? sA[i0] : sB[i0], s1 = (k < 2) ? sA[i0 + 1] : sB[i0 + 1];
-      const uint32_t g0 = (k < 2) ? dA[i0] : dB[i0], g1 = (k < 2) ? dA[i0 + 1] : dB[i0 + 1];
+    for (int k = 0; k < 2; ++k) {
+      const uint32_t s0 = s[4 * n + 2 * k], s1 = s[4 * n + 2 * k + 1];
+      const uint32_t g0 = d[4 * n + 2 * k], g1 = d[4 * n + 2 * k + 1];
       // exact integer logits (see the forward kernel), then scale and subtract the saved LSE
       float2 v = make_float2(__uint_as_float(s0 + 0x4B400000u), __uint_as_float(s1 + 0x4B400000u));
       v = __fadd2_rn(v, negM2);
@@ -107,23 +120,25 @@ __device__ __forceinline__ void bwd_block(const uint32_t (&sA)[16], const uint32
       v = __fmul2_rn(v, s2);
       v = __ffma2_rn(v, rc.a2[k], KV_PASS ? l2 : rc.nlse2[k]);
       if (MASKED) {
-        // visible columns of row k inside this block: lo[k] <= 8n + e < hi[k]
         if (8 * n < lo[k] || 8 * n >= hi[k]) v.x = -INFINITY;
         if (8 * n + 1 < lo[k] || 8 * n + 1 >= hi[k]) v.y = -INFINITY;
       }
       const float p0 = fast_exp2(v.x), p1 = fast_exp2(v.y);
       float2 dd = __fadd2_rn(make_float2(__uint_as_float(g0), __uint_as_float(g1)), KV_PASS ? d2 : rc.ndelta2[k]);
       dd = __fmul2_rn(make_float2(p0, p1), dd);
-      const uint32_t wp = H16::pack(p0, p1);          // P rounded to 16 bit (quant_flash_attn.py:156)
-      const uint32_t wd = H16::pack(dd.x, dd.y);      // dS rounded to 16 bit (quant_flash_attn.py:159-160)
-      if (k < 2) { pA[2 * n + (k & 1)] = wp; gA[2 * n + (k & 1)] = wd; }
-      else { pB[2 * n + (k & 1)] = wp; gB[2 * n + (k & 1)] = wd; }
+      pw[2 * n + k] = H16::pack(p0, p1);              // P rounded to 16 bit (quant_flash_attn.py:156)
+      gw[2 * n + k] = H16::pack(dd.x, dd.y);          // dS rounded to 16 bit (quant_flash_attn.py:159-160)
     }
   }
 }
 
+__device__ __forceinline__ void tmem_st_16x128b_x2(uint32_t taddr, const uint32_t (&r)[4]) {
+  asm volatile("tcgen05.st.sync.aligned.16x128b.x2.b32 [%0], {%1, %2, %3, %4};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]) : "memory");
+}
+
 template <typename T, int D, bool KV_PASS>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(BwdTcCfg<D>::THREADS, 1)
 attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_constant__ CUtensorMap tmXh,
                    const __grid_constant__ CUtensorMap tmYc, const __grid_constant__ CUtensorMap tmYa,
                    const __grid_constant__ CUtensorMap tmYb, const TcBwdParams p) {
@@ -135,7 +150,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
   auto BAR = [&](int i) { return sbase + C::BAR_OFF + 8u * i; };
   constexpr int B_XFULL = 0;
   constexpr int B_YFULL = 1, B_YEMPTY = B_YFULL + C::STAGES, B_MFULL = B_YEMPTY + C::STAGES;
-  constexpr int B_T1 = B_MFULL + C::STAGES, B_T2 = B_T1 + 1, B_PD = B_T2 + 1, B_ACC = B_PD + 1;
+  constexpr int B_T1 = B_MFULL + C::STAGES, B_T2 = B_T1 + 1, B_ACC = B_T2 + 1, B_PD = B_ACC + 1;   // B_PD + k-step
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::MISC_OFF);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::MISC_OFF + 4);
 
@@ -162,12 +177,12 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
     for (int i = 0; i < C::STAGES; ++i) {
       mbar_init(BAR(B_YFULL + i), 1);
       mbar_init(BAR(B_YEMPTY + i), 1);
-      mbar_init(BAR(B_MFULL + i), 32);
+      mbar_init(BAR(B_MFULL + i), 1);
     }
     mbar_init(BAR(B_T1), 1);
     mbar_init(BAR(B_T2), 1);
-    mbar_init(BAR(B_PD), 128);
     mbar_init(BAR(B_ACC), 1);
+    for (int i = 0; i < C::KSTEPS; ++i) mbar_init(BAR(B_PD + i), C::SOFTMAX_WARPS / 2);   // the 8 warps of a column half
     fence_barrier_init();
   }
   if (warp == 2) {
@@ -183,6 +198,15 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
   // queries index LSE / delta: they are the columns in pass KV, the rows in pass Q
   const int64_t lse0 = static_cast<int64_t>(bh) * p.lse_stride;
 
+  if (warp < 4) {
+  // Register hand-over between warpgroups: the control warps give registers to the softmax warps.
+  // setmaxnreg.inc BLOCKS until the CTA's pool (threads x registers the kernel was launched with) has enough
+  // free registers, so the two budgets must fit that pool or the softmax warps would wait forever; the host
+  // side refuses to launch if the compiled kernel has fewer registers per thread than LAUNCH_REGS.
+  static_assert(128 * C::CONTROL_REGS + C::SOFTMAX_WARPS * 32 * C::SOFTMAX_REGS <= C::THREADS * C::LAUNCH_REGS,
+                "setmaxnreg budgets exceed the CTA's registers");
+  static_assert(C::CONTROL_REGS == 56 && C::SOFTMAX_REGS == 104, "keep the asm immediates below in step");
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
   if (warp == 0) {
     // ================================================================ producer
     if (lane == 0) {
@@ -209,7 +233,9 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
         }
       }
       // per-column constants (the stage's previous readers are done: Y-empty is committed after the step's last MMA,
-      // which is issued after the softmax warps finished the step)
+      // which is issued after the softmax warps finished the step).  Layout for the softmax threads: thread q of a
+      // quad owns columns 8n+2q, 8n+2q+1; the constants of the two column groups of a 16-column block are packed
+      // into five 16-byte words {z}, {-sum}, {s}, {-lse*log2e}, {-delta}
       float* meta = reinterpret_cast<float*>(smem + C::M_OFF + st * C::M_BYTES);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -226,13 +252,16 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
             nd = -p.delta[lse0 + c];
           }
         }
-        meta[col] = z;
-        meta[128 + col] = ns;
-        meta[256 + col] = s;
-        meta[384 + col] = nl;      // columns past the end: -inf reference -> P = 0 (pass Q masks them by index)
-        meta[512 + col] = nd;
+        const int n8 = col >> 3, qq = (col >> 1) & 3, e = col & 1;
+        float* dst = meta + (((n8 >> 1) * 4 + qq) * 5) * 4 + (n8 & 1) * 2 + e;
+        dst[0] = z;
+        dst[4] = ns;
+        dst[8] = s;
+        dst[12] = nl;      // columns past the end: -inf reference -> P = 0 (pass Q masks them by index)
+        dst[16] = nd;
       }
-      mbar_arrive(BAR(B_MFULL + st));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(BAR(B_MFULL + st));
     }
   } else if (warp == 1) {
     // ================================================================ MMA issuer (one thread)
@@ -250,7 +279,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
         ok = mbar_wait(BAR(B_YFULL + st), (it / C::STAGES) & 1, abort_flag, p.epoch);
         if (!ok) break;
         tc_fence_after_sync();
-        // T1 = Xc Yc^T (int8), T2 = Xh Ya^T (16 bit, K-major x K-major)
+        // T1 = Xc Yc^T (int8), T2 = Xh Ya^T (16 bit, K-major x K-major).  They overwrite the P / dS of the previous
+        // step: the tensor pipe runs MMAs in issue order, so they start after that step's accumulating MMAs
         {
           const uint64_t da = make_smem_desc(sbase + C::XC_OFF, 16, 8 * D, kCSwz);
           const uint64_t db = make_smem_desc(stage, 16, 8 * D, kCSwz);
@@ -267,42 +297,44 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
           }
           mma_commit(BAR(B_T2));
         }
-        // accumulate with P / dS read from tensor memory
-        ok = mbar_wait(BAR(B_PD), it & 1, abort_flag, p.epoch);
-        if (!ok) break;
-        tc_fence_after_sync();
-        if (KV_PASS) {
-          // acc1 (dV) += P^T dO : right operand = the Ya tile (dO) viewed MN-major
-          const uint64_t db = make_smem_desc(stage + C::C_BYTES, C::PANEL_BYTES, 1024, kSwizzle128B);
-#pragma unroll
-          for (int k = 0; k < 8; ++k)
-            mma_f16_ts(tmem + C::ACC1_COL, tmem + C::T1_COL + k * 8, desc_advance(db, k * 2048), kIdescAcc,
-                       (it > 0 || k > 0) ? 1u : 0u);
-        }
-        {
+        // accumulate with P / dS read from tensor memory, one 16-column k-step at a time as the softmax warps hand
+        // the blocks over (the two column halves advance side by side)
+        const uint64_t db1 = make_smem_desc(stage + C::C_BYTES, C::PANEL_BYTES, 1024, kSwizzle128B);               // dO (pass KV)
+        const uint64_t db2 = make_smem_desc(stage + C::C_BYTES + C::H_BYTES, C::PANEL_BYTES, 1024, kSwizzle128B);  // Q^ or K^
+#pragma unroll 1
+        for (int i = 0; i < C::KSTEPS; ++i) {
+          const int kk = (i & 1) * 4 + (i >> 1);
+          ok = mbar_wait(BAR(B_PD + kk), it & 1, abort_flag, p.epoch);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t acc_flag = (it > 0 || i > 0) ? 1u : 0u;
+          if (KV_PASS)      // acc1 (dV) += P^T dO : right operand = the Ya tile (dO) viewed MN-major
+            mma_f16_ts(tmem + C::ACC1_COL, tmem + C::T1_COL + C::p_col(kk), desc_advance(db1, kk * 2048), kIdescAcc, acc_flag);
           // acc2 (dK or dQ) += dS Yb : Yb = Q^ (pass KV) or K^ (pass Q), MN-major
-          const uint64_t db = make_smem_desc(stage + C::C_BYTES + C::H_BYTES, C::PANEL_BYTES, 1024, kSwizzle128B);
-#pragma unroll
-          for (int k = 0; k < 8; ++k)
-            mma_f16_ts(tmem + C::ACC2_COL, tmem + C::T2_COL + k * 8, desc_advance(db, k * 2048), kIdescAcc,
-                       (it > 0 || k > 0) ? 1u : 0u);
+          mma_f16_ts(tmem + C::ACC2_COL, tmem + C::T2_COL + C::p_col(kk), desc_advance(db2, kk * 2048), kIdescAcc, acc_flag);
         }
+        if (!ok) break;
         mma_commit(BAR(B_YEMPTY + st));
         if (it == n_steps - 1) mma_commit(BAR(B_ACC));
       }
     }
-  } else if (warp >= 4) {
+  }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
     // ================================================================ softmax-side math
+    // warp (wq, hh, ch): rows 32*wq + 16*hh .. +15 of the tile, columns 64*ch .. +63
+    const int sw = warp - 4;
     const int wq = warp & 3;
+    const int hh = (sw >> 2) & 1;
+    const int ch = sw >> 3;
     const int g = lane >> 2, q = lane & 3;
-    const uint32_t quarter = static_cast<uint32_t>(wq * 32) << 16;
-    constexpr uint32_t kLane16 = 16u << 16;
-    const uint32_t tT1 = tmem + quarter + C::T1_COL, tT2 = tmem + quarter + C::T2_COL;
-    int rowk[4];
-    BwdRow4 rc;
+    const uint32_t lanes = static_cast<uint32_t>(wq * 32 + hh * 16) << 16;
+    const uint32_t tT1 = tmem + lanes + C::T1_COL + 64 * ch, tT2 = tmem + lanes + C::T2_COL + 64 * ch;
+    int rowk[2];
+    BwdRow2 rc;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      rowk[k] = r0 + wq * 32 + g + 8 * k;
+    for (int k = 0; k < 2; ++k) {
+      rowk[k] = r0 + wq * 32 + hh * 16 + g + 8 * k;
       float A = 0.f, z = 0.f, a = 0.f, nl = -INFINITY, nd = 0.f;
       if (rowk[k] < p.rows_total) {
         const int64_t tk = tok_r0 + rowk[k];
@@ -332,53 +364,47 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
-      const float* meta = reinterpret_cast<const float*>(smem + C::M_OFF + st * C::M_BYTES) + 2 * q;
-      // visible column range of each row, relative to (tile start + 2q)
-      int lo[4], hi[4];
+      const float4* meta = reinterpret_cast<const float4*>(smem + C::M_OFF + st * C::M_BYTES) + (16 * ch + q) * 5;
+      // visible column range of each row, relative to (tile start + 64*ch + 2q)
+      int lo[2], hi[2];
       bool any_masked = false;
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
+      for (int k = 0; k < 2; ++k) {
         int first = 0, last = p.cols_total - c0;                  // [first, last) in tile coordinates
         if (p.causal) {
           if (KV_PASS) first = max(first, rowk[k] - c0);          // query >= token
           else last = min(last, rowk[k] + 1 - c0);                // token <= query
         }
         any_masked |= (first > 0) || (last < C::BN);
-        lo[k] = first - 2 * q;
-        hi[k] = last - 2 * q;
+        lo[k] = first - 64 * ch - 2 * q;
+        hi[k] = last - 64 * ch - 2 * q;
       }
       const bool masked = __any_sync(0xffffffffu, any_masked);
+      uint32_t sreg[2][8], dreg[2][8];
+      tmem_ld_16x256b_x2(tT1, sreg[0]);
+      tmem_ld_16x256b_x2(tT2, dreg[0]);
 #pragma unroll
       for (int blk = 0; blk < 4; ++blk) {
-        uint32_t sA[16], sB[16], dA[16], dB[16];
-        tmem_ld_16x256b_x4(tT1 + blk * 32, sA);
-        tmem_ld_16x256b_x4(tT1 + kLane16 + blk * 32, sB);
-        tmem_ld_16x256b_x4(tT2 + blk * 32, dA);
-        tmem_ld_16x256b_x4(tT2 + kLane16 + blk * 32, dB);
-        tmem_wait_ld();
-        int lo_b[4], hi_b[4];
+        tmem_wait_ld_use(sreg[blk & 1], dreg[blk & 1]);
+        if (blk + 1 < 4) {
+          tmem_ld_16x256b_x2(tT1 + (blk + 1) * 16, sreg[(blk + 1) & 1]);
+          tmem_ld_16x256b_x2(tT2 + (blk + 1) * 16, dreg[(blk + 1) & 1]);
+        }
+        int lo_b[2], hi_b[2];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) { lo_b[k] = lo[k] - blk * 32; hi_b[k] = hi[k] - blk * 32; }
-        uint32_t pA[8], pB[8], gA[8], gB[8];
-        if (masked) bwd_block<T, KV_PASS, true>(sA, sB, dA, dB, meta + blk * 32, lo_b, hi_b, rc, pA, pB, gA, gB);
-        else bwd_block<T, KV_PASS, false>(sA, sB, dA, dB, meta + blk * 32, lo_b, hi_b, rc, pA, pB, gA, gB);
-        // P / dS of this block go to columns [16 blk, 16 blk + 16) of T1 / T2: already consumed above
-        asm volatile("tcgen05.st.sync.aligned.16x128b.x4.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-                     ::"r"(tT1 + blk * 16), "r"(pA[0]), "r"(pA[1]), "r"(pA[2]), "r"(pA[3]), "r"(pA[4]), "r"(pA[5]),
-                       "r"(pA[6]), "r"(pA[7]) : "memory");
-        asm volatile("tcgen05.st.sync.aligned.16x128b.x4.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-                     ::"r"(tT1 + kLane16 + blk * 16), "r"(pB[0]), "r"(pB[1]), "r"(pB[2]), "r"(pB[3]), "r"(pB[4]),
-                       "r"(pB[5]), "r"(pB[6]), "r"(pB[7]) : "memory");
-        asm volatile("tcgen05.st.sync.aligned.16x128b.x4.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-                     ::"r"(tT2 + blk * 16), "r"(gA[0]), "r"(gA[1]), "r"(gA[2]), "r"(gA[3]), "r"(gA[4]), "r"(gA[5]),
-                       "r"(gA[6]), "r"(gA[7]) : "memory");
-        asm volatile("tcgen05.st.sync.aligned.16x128b.x4.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-                     ::"r"(tT2 + kLane16 + blk * 16), "r"(gB[0]), "r"(gB[1]), "r"(gB[2]), "r"(gB[3]), "r"(gB[4]),
-                       "r"(gB[5]), "r"(gB[6]), "r"(gB[7]) : "memory");
+        for (int k = 0; k < 2; ++k) { lo_b[k] = lo[k] - blk * 16; hi_b[k] = hi[k] - blk * 16; }
+        uint32_t pw[4], gw[4];
+        if (masked) bwd_block<T, KV_PASS, true>(sreg[blk & 1], dreg[blk & 1], meta + blk * 20, lo_b, hi_b, rc, pw, gw);
+        else bwd_block<T, KV_PASS, false>(sreg[blk & 1], dreg[blk & 1], meta + blk * 20, lo_b, hi_b, rc, pw, gw);
+        // P / dS of this block go to 32-bit columns [8 blk, 8 blk + 8) of this half of T1 / T2: the int32 / fp32
+        // values that lived there were consumed by this warp in an earlier (or this) block
+        tmem_st_16x128b_x2(tT1 + blk * 8, pw);
+        tmem_st_16x128b_x2(tT2 + blk * 8, gw);
+        tmem_wait_st();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(BAR(B_PD + 4 * ch + blk));
       }
-      tmem_wait_st();
-      tc_fence_before_sync();
-      mbar_arrive(BAR(B_PD));
     }
     // ---------------- epilogue: accumulators -> 16 bit.  dK and dQ carry sm_scale (quant_flash_attn.py:161,164)
     if (ok && n_steps > 0) {
@@ -387,31 +413,30 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
     }
     if (ok) {
       tc_fence_after_sync();
-      const int row = r0 + wq * 32 + lane;
+      // this warp writes its 16 rows x D/2 columns of each accumulator
       for (int which = KV_PASS ? 0 : 1; which < 2; ++which) {
-        const uint32_t tA = tmem + quarter + (which == 0 ? C::ACC1_COL : C::ACC2_COL);
+        const uint32_t tA = tmem + lanes + (which == 0 ? C::ACC1_COL : C::ACC2_COL) + ch * (D / 2);
         const float scale = (which == 0) ? 1.0f : p.sm_scale;
         const int64_t* os = (which == 0) ? p.out1_stride : p.out2_stride;
-        T* orow = static_cast<T*>(which == 0 ? p.out1 : p.out2) + b * os[0] + h * os[1] + static_cast<int64_t>(row) * os[2];
+        T* obase = static_cast<T*>(which == 0 ? p.out1 : p.out2) + b * os[0] + h * os[1] + ch * (D / 2) + 2 * q;
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t oreg[32];
+        for (int c = 0; c < D / 64; ++c) {
+          uint32_t oreg[16];
           if (n_steps > 0) {
-            tmem_ld32(tA + c * 32, oreg);
+            tmem_ld_16x256b_x4(tA + c * 32, oreg);
             tmem_wait_ld();
           } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) oreg[i] = 0u;       // a row block that meets no column tile: zero gradient
+            for (int i = 0; i < 16; ++i) oreg[i] = 0u;       // a row block that meets no column tile: zero gradient
           }
-          if (row < p.rows_total) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              uint4 v;
-              v.x = H16::pack(__uint_as_float(oreg[i]) * scale, __uint_as_float(oreg[i + 1]) * scale);
-              v.y = H16::pack(__uint_as_float(oreg[i + 2]) * scale, __uint_as_float(oreg[i + 3]) * scale);
-              v.z = H16::pack(__uint_as_float(oreg[i + 4]) * scale, __uint_as_float(oreg[i + 5]) * scale);
-              v.w = H16::pack(__uint_as_float(oreg[i + 6]) * scale, __uint_as_float(oreg[i + 7]) * scale);
-              *reinterpret_cast<uint4*>(orow + c * 32 + i) = v;
+          for (int k = 0; k < 2; ++k) {
+            if (rowk[k] < p.rows_total) {
+              T* orow = obase + static_cast<int64_t>(rowk[k]) * os[2] + c * 32;
+#pragma unroll
+              for (int n = 0; n < 4; ++n)
+                *reinterpret_cast<uint32_t*>(orow + 8 * n) =
+                    H16::pack(__uint_as_float(oreg[4 * n + 2 * k]) * scale, __uint_as_float(oreg[4 * n + 2 * k + 1]) * scale);
             }
           }
         }
@@ -480,6 +505,10 @@ static int launch_bwd_tc(const QfaBwdArgs& a, cudaStream_t stream) {
   QFA_CUDA_TRY(cudaGetDevice(&devid));
   if (devid < 64 && !attr_done[devid]) {
     QFA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+    // the register hand-over inside the kernel assumes this many registers per thread at launch
+    cudaFuncAttributes fa;
+    QFA_CUDA_TRY(cudaFuncGetAttributes(&fa, kern));
+    if (fa.numRegs < C::LAUNCH_REGS) return cuda_fail(cudaErrorLaunchOutOfResources, "backward kernel register pool");
     attr_done[devid] = true;
   }
   const int64_t n_ctas = ((Sx + C::BM - 1) / C::BM) * a.B * a.H;
