@@ -52,6 +52,23 @@ struct TcBwdParams {
   int32_t* status;
 };
 
+// Optional timeline tracing for development builds (-DQFA_TC_TRACE): CTA 0 writes clock64() stamps of its
+// first 16 steps into the buffer passed as `status` (interpreted as long long[2][16][16]).
+#ifdef QFA_TC_TRACE
+#ifndef QFA_TRACE_KV
+#define QFA_TRACE_KV 1
+#endif
+#define QFA_BTRACE(role, it, idx)                                                                   \
+  do {                                                                                              \
+    if (KV_PASS == bool(QFA_TRACE_KV) && blockIdx.x == 0 && (it) < 16 && p.status)                  \
+      reinterpret_cast<long long*>(p.status)[((role) * 16 + (it)) * 16 + (idx)] = clock64();        \
+  } while (0)
+#else
+#define QFA_BTRACE(role, it, idx) \
+  do {                            \
+  } while (0)
+#endif
+
 template <int D>
 struct BwdTcCfg {
   static constexpr int BM = 128, BN = 128, STAGES = 2;
@@ -67,7 +84,8 @@ struct BwdTcCfg {
   static constexpr int M_OFF = ST_OFF + STAGES * ST_BYTES;
   static constexpr int BAR_OFF = M_OFF + STAGES * M_BYTES;
   static constexpr int KSTEPS = BN / 16;               // 16-column blocks = k-steps of the accumulating MMAs
-  static constexpr int NBARS = 1 + 3 * STAGES + 3 + KSTEPS;
+  static constexpr int HANDOFFS = KSTEPS / 2;           // P / dS are handed to the MMA issuer 32 columns at a time
+  static constexpr int NBARS = 1 + 3 * STAGES + 3 + HANDOFFS;
   static constexpr int MISC_OFF = BAR_OFF + NBARS * 8;
   static constexpr int SMEM = MISC_OFF + 16 + 1024;
   static constexpr int SOFTMAX_WARPS = 16;
@@ -182,7 +200,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
     mbar_init(BAR(B_T1), 1);
     mbar_init(BAR(B_T2), 1);
     mbar_init(BAR(B_ACC), 1);
-    for (int i = 0; i < C::KSTEPS; ++i) mbar_init(BAR(B_PD + i), C::SOFTMAX_WARPS / 2);   // the 8 warps of a column half
+    for (int i = 0; i < C::HANDOFFS; ++i) mbar_init(BAR(B_PD + i), C::SOFTMAX_WARPS / 2);   // the 8 warps of a column half
     fence_barrier_init();
   }
   if (warp == 2) {
@@ -276,9 +294,11 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
       for (int it = 0; it < n_steps && ok; ++it) {
         const int st = it % C::STAGES;
         const uint32_t stage = sbase + C::ST_OFF + st * C::ST_BYTES;
+        QFA_BTRACE(1, it, 0);
         ok = mbar_wait(BAR(B_YFULL + st), (it / C::STAGES) & 1, abort_flag, p.epoch);
         if (!ok) break;
         tc_fence_after_sync();
+        QFA_BTRACE(1, it, 1);
         // T1 = Xc Yc^T (int8), T2 = Xh Ya^T (16 bit, K-major x K-major).  They overwrite the P / dS of the previous
         // step: the tensor pipe runs MMAs in issue order, so they start after that step's accumulating MMAs
         {
@@ -297,23 +317,33 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
           }
           mma_commit(BAR(B_T2));
         }
+        QFA_BTRACE(1, it, 2);
         // accumulate with P / dS read from tensor memory, one 16-column k-step at a time as the softmax warps hand
         // the blocks over (the two column halves advance side by side)
         const uint64_t db1 = make_smem_desc(stage + C::C_BYTES, C::PANEL_BYTES, 1024, kSwizzle128B);               // dO (pass KV)
         const uint64_t db2 = make_smem_desc(stage + C::C_BYTES + C::H_BYTES, C::PANEL_BYTES, 1024, kSwizzle128B);  // Q^ or K^
-#pragma unroll 1
-        for (int i = 0; i < C::KSTEPS; ++i) {
-          const int kk = (i & 1) * 4 + (i >> 1);
-          ok = mbar_wait(BAR(B_PD + kk), it & 1, abort_flag, p.epoch);
+#pragma unroll
+        for (int i = 0; i < C::HANDOFFS; ++i) {
+          const int hf = (i & 1) * 2 + (i >> 1);           // handoff index: column half * 2 + 32-column part
+          const int kk0 = 2 * hf;                          // its two k-steps
+          ok = mbar_wait(BAR(B_PD + hf), it & 1, abort_flag, p.epoch);
           if (!ok) break;
           tc_fence_after_sync();
-          const uint32_t acc_flag = (it > 0 || i > 0) ? 1u : 0u;
-          if (KV_PASS)      // acc1 (dV) += P^T dO : right operand = the Ya tile (dO) viewed MN-major
-            mma_f16_ts(tmem + C::ACC1_COL, tmem + C::T1_COL + C::p_col(kk), desc_advance(db1, kk * 2048), kIdescAcc, acc_flag);
+          QFA_BTRACE(1, it, 3 + i);
+          if (KV_PASS) {    // acc1 (dV) += P^T dO : right operand = the Ya tile (dO) viewed MN-major
+#pragma unroll
+            for (int kk = kk0; kk < kk0 + 2; ++kk)
+              mma_f16_ts(tmem + C::ACC1_COL, tmem + C::T1_COL + C::p_col(kk), desc_advance(db1, kk * 2048), kIdescAcc,
+                         (it > 0 || i > 0 || kk > kk0) ? 1u : 0u);
+          }
           // acc2 (dK or dQ) += dS Yb : Yb = Q^ (pass KV) or K^ (pass Q), MN-major
-          mma_f16_ts(tmem + C::ACC2_COL, tmem + C::T2_COL + C::p_col(kk), desc_advance(db2, kk * 2048), kIdescAcc, acc_flag);
+#pragma unroll
+          for (int kk = kk0; kk < kk0 + 2; ++kk)
+            mma_f16_ts(tmem + C::ACC2_COL, tmem + C::T2_COL + C::p_col(kk), desc_advance(db2, kk * 2048), kIdescAcc,
+                       (it > 0 || i > 0 || kk > kk0) ? 1u : 0u);
         }
         if (!ok) break;
+        QFA_BTRACE(1, it, 11);
         mma_commit(BAR(B_YEMPTY + st));
         if (it == n_steps - 1) mma_commit(BAR(B_ACC));
       }
@@ -358,12 +388,16 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
     for (int it = 0; it < n_steps && ok; ++it) {
       const int st = it % C::STAGES;
       const int c0 = (j_begin + it) * C::BN;
+      const bool tr = (sw == 0 && lane == 0);
+      if (tr) QFA_BTRACE(0, it, 0);
       ok = mbar_wait(BAR(B_MFULL + st), (it / C::STAGES) & 1, abort_flag, p.epoch);
       if (ok) ok = mbar_wait(BAR(B_T1), it & 1, abort_flag, p.epoch);
+      if (tr) QFA_BTRACE(0, it, 1);
       if (ok) ok = mbar_wait(BAR(B_T2), it & 1, abort_flag, p.epoch);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
+      if (tr) QFA_BTRACE(0, it, 2);
       const float4* meta = reinterpret_cast<const float4*>(smem + C::M_OFF + st * C::M_BYTES) + (16 * ch + q) * 5;
       // visible column range of each row, relative to (tile start + 64*ch + 2q)
       int lo[2], hi[2];
@@ -386,6 +420,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
 #pragma unroll
       for (int blk = 0; blk < 4; ++blk) {
         tmem_wait_ld_use(sreg[blk & 1], dreg[blk & 1]);
+        if (tr) QFA_BTRACE(0, it, 3 + 2 * blk);
         if (blk + 1 < 4) {
           tmem_ld_16x256b_x2(tT1 + (blk + 1) * 16, sreg[(blk + 1) & 1]);
           tmem_ld_16x256b_x2(tT2 + (blk + 1) * 16, dreg[(blk + 1) & 1]);
@@ -400,10 +435,14 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
         // values that lived there were consumed by this warp in an earlier (or this) block
         tmem_st_16x128b_x2(tT1 + blk * 8, pw);
         tmem_st_16x128b_x2(tT2 + blk * 8, gw);
-        tmem_wait_st();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(BAR(B_PD + 4 * ch + blk));
+        if (blk & 1) {
+          // two blocks = two k-steps of the accumulating MMAs are ready
+          tmem_wait_st();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(BAR(B_PD + 2 * ch + (blk >> 1)));
+          if (tr) QFA_BTRACE(0, it, 4 + 2 * blk);
+        }
       }
     }
     // ---------------- epilogue: accumulators -> 16 bit.  dK and dQ carry sm_scale (quant_flash_attn.py:161,164)
@@ -450,7 +489,9 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
     tc_fence_after_sync();
     tmem_dealloc(tmem, C::TMEM_COLS);
   }
+#ifndef QFA_TC_TRACE
   if (tid == 0 && *abort_flag && p.status) *p.status = QFA_STATUS_WAIT_TIMEOUT;
+#endif
 }
 
 static std::atomic<unsigned int> g_bwd_epoch{0x40000000u};
