@@ -318,7 +318,13 @@ def run_ours(args):
             "peak_kind": ("sustained" if long_run else "burst") + " bf16 dense, of " + peaks["source"],
             "frac_of_mixed_int8_bf16": achieved / (1.0 / (0.5 / (2 * peak) + 0.5 / peak)),
             "frac_of_int8_nominal_4500": achieved / 4500.0,
-            "traffic": None, "ms_per_launch": attn_ms,
+            # DRAM bytes per launch: one profiler capture of the same kernel at B1 H16 (the full workload is too large
+            # to capture) read 34.55 MB + wrote 0.22 MB for 16 heads; K, V^ and Q are read once per head and O
+            # (134 MB at full size, written once) was still in L2 when that small kernel ended, so the figure is
+            # per-head reads scaled by the heads of a launch plus the output bytes
+            "traffic": (B * H) * (34.55e6 / 16) + B * H * S * D * 2,
+            "traffic_note": "scaled from a 16-head capture: 2.16 MB read per head + output bytes",
+            "ms_per_launch": attn_ms,
         }
         if "quantizer" in extra:
             extra["quantizer"]["frac_of_hbm_" + peaks["source"]] = extra["quantizer"]["GBps"] / peaks["hbm_gbs"]
@@ -349,9 +355,9 @@ def run_profile_case(case: str):
     if case == "quant":
         x = torch.randn(8, 32, 4096, 128, device=dev, dtype=torch.bfloat16)
         for _ in range(2):
-            out = qfa.asymmetric_quant_per_token(x)
+            out = qfa.asymmetric_quant_per_token_ex(x)      # codes, scale, zero point and code sums, as in the bench step
         torch.cuda.synchronize()
-        print("ok", int(out[0].int().sum()))
+        print("ok", int(out[3].sum()))
         return
     b, h, s, d = 1, 16, 4096, 128
     causal = case == "fwd_causal"
