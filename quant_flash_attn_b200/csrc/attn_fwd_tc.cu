@@ -377,10 +377,15 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     // overflowed its 16-bit type); beyond that the tile is recomputed from S, which is still intact
     constexpr float kInRegMax = std::is_same<T, __half>::value ? 15.0f : 100.0f;
     // how far (in powers of two) a tile may exceed the reference before the reference is raised.  P is stored in
-    // T: fp16 keeps P <= 2^8 well inside its range; bf16 has fp32's exponent range and constant relative
+    // T: fp16 keeps P <= 2^14 inside its range; bf16 has fp32's exponent range and constant relative
     // precision, so P, l and O may carry a factor up to 2^64 and the rescale path becomes rare even for
     // heavy-tailed logits
-    constexpr float kGrow = std::is_same<T, __half>::value ? 8.0f : 64.0f;
+    constexpr float kGrow = std::is_same<T, __half>::value ? 14.0f : 64.0f;
+    // a reference is set this far above the maximum it is derived from: row maxima of later tiles usually exceed
+    // it by a few standard deviations of the logits, and starting above moves many rows out of the rescale path.
+    // The result does not depend on the reference; P merely starts at 2^-margin instead of 1 (fp16 keeps its
+    // largest P well inside the normal range)
+    constexpr float kMargin = std::is_same<T, __half>::value ? 4.0f : 32.0f;
     float ref[2] = {0.f, 0.f}, l_run[2] = {0.f, 0.f};
     const int my_n = n_t[t];
     bool ok = true;
@@ -446,7 +451,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           quad_max();
 #pragma unroll
           for (int k = 0; k < 2; ++k) {
-            ref[k] = (emax[k] == -INFINITY) ? 0.f : emax[k];
+            ref[k] = (emax[k] == -INFINITY) ? 0.f : emax[k] + kMargin;
             rc.nref2[k] = make_float2(-ref[k], -ref[k]);
             emax[k] = -INFINITY;
           }
@@ -462,7 +467,15 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           bool redo = false;
 #pragma unroll
           for (int k = 0; k < 2; ++k) {
-            kf[k] = (emax[k] > kGrow) ? ceilf(emax[k]) : 0.f;      // whole number: 2^-kf is exact
+            // raise by a whole number (2^-kf is exact) to kMargin above the tile's maximum.  Rows whose P is
+            // rescaled in registers need a representable factor, so their step is capped; rows that force the
+            // recompute may step further: a factor that underflows to zero then drops contributions that are
+            // below 2^-24 of the new ones anyway
+            kf[k] = 0.f;
+            if (emax[k] > kGrow) {
+              kf[k] = ceilf(emax[k]) + kMargin;
+              if (emax[k] <= kInRegMax) kf[k] = fminf(kf[k], 120.0f);
+            }
             factor[k] = fast_exp2(-kf[k]);
             redo |= emax[k] > kInRegMax;
           }
