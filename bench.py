@@ -2,7 +2,7 @@
 """Benchmark of the quantized-attention hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-    python bench.py --profile-case quant|fwd|fwd_causal|bwd     (small fixed case for a profiler capture)
+    python bench.py --profile-case quant|fwd|fwd_causal|bwd|shortq     (small fixed case for a profiler capture)
 
 Workload (N=1): INT8 attention forward at B=4 H=32 S=4096 D=128, bf16 inputs ~N(0,1) with 1 % of
 the channels scaled x20, seeded, non-causal.  One step = quantize Q, K, V per token (3 launches of
@@ -359,6 +359,19 @@ def run_profile_case(case: str):
         torch.cuda.synchronize()
         print("ok", int(out[3].sum()))
         return
+    if case == "shortq":
+        # the reference's own regime (test_speed.py:69-77) at a quarter of its batch: Z64 H16 NQ16 NKV2048 D128 fp16
+        z, hh, nq, nkv, dd = 64, 16, 16, 2048, 128
+        q = torch.randn(z, hh, nq, dd, device=dev, dtype=torch.float16, requires_grad=True)
+        kv = torch.randn(z, hh, nkv, dd, device=dev, dtype=torch.float16, requires_grad=True)
+        go = torch.randn_like(q)
+        kvq = qfa.asymmetric_quant_per_token(kv.detach())
+        for _ in range(2):
+            o = qfa.quant_flash_attn(q, kv, kvq, 1.0 / math.sqrt(dd))
+            o.backward(go)
+        torch.cuda.synchronize()
+        print("ok", float(kv.grad.float().abs().mean()))
+        return
     b, h, s, d = 1, 16, 4096, 128
     causal = case == "fwd_causal"
     sm = 1.0 / math.sqrt(d)
@@ -381,7 +394,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--profile-case", default=None, choices=["quant", "fwd", "fwd_causal", "bwd"])
+    ap.add_argument("--profile-case", default=None, choices=["quant", "fwd", "fwd_causal", "bwd", "shortq"])
     args = ap.parse_args()
     if args.profile_case:
         run_profile_case(args.profile_case)

@@ -8,12 +8,14 @@
 //   * split each 64-token K/V tile BY COLUMNS among the 4 warps (16 tokens each), every warp working on all
 //     query rows with its own online-softmax state; the warps' partial results are merged once at the end,
 //   * dequantize K/V exactly as the reference ((code - zp) * scale rounded to the 16-bit dtype,
-//     quant_flash_attn.py:65-66) while staging it into shared memory; the next tile's codes are already in
-//     flight in registers,
+//     quant_flash_attn.py:65-66) while staging it into shared memory; the codes of the next four tiles are
+//     in flight as bulk copies into a shared-memory ring (the kernels are bound by the latency of that stream:
+//     with one tile in flight per CTA they reached a fifth of the HBM bandwidth),
 //   * in the backward keep dQ in registers for the whole walk (no atomics, no scratch) and write each
 //     dKV tile exactly once, dKV = dV + sm_scale*dK (quant_flash_attn.py:161).
 // REF mode only (16-bit Q, K and V the same tensor), Sq <= 32.
 #include "qfa_common.cuh"
+#include "sm100_ptx.cuh"
 
 namespace qfa {
 
@@ -37,6 +39,7 @@ struct ShortQDev {
   int64_t lse_stride;
   int H, Sq, Skv;
   float sm_scale;
+  int32_t* status;
 };
 
 template <int D, int MT>
@@ -52,12 +55,19 @@ struct SqCfg {
   static constexpr int KV_OFF_BWD = DO_OFF + ROWS * T_STRIDE;
   static constexpr int TILES_FWD = KV_OFF_FWD + BN * T_STRIDE;
   static constexpr int MERGE_FWD = 4 * ROWS * D * 4 + 4 * ROWS * 8;      // O partials + (m, l) per warp
-  static constexpr int SMEM_FWD = TILES_FWD > MERGE_FWD ? TILES_FWD : MERGE_FWD;
   static constexpr int DS_STRIDE = 2 * ROWS + 16;            // dS^T rows [kv][q], 16 bit
   static constexpr int DS_OFF = KV_OFF_BWD + BN * T_STRIDE;
   static constexpr int TILES_BWD = DS_OFF + BN * DS_STRIDE;
   static constexpr int MERGE_BWD = 4 * ROWS * D * 4;
-  static constexpr int SMEM_BWD = TILES_BWD > MERGE_BWD ? TILES_BWD : MERGE_BWD;
+  // ring of raw code tiles filled by bulk copies + (scale, zero point) per key + one mbarrier per stage; it sits
+  // behind the larger of the tile / merge regions so that the final merge never overlaps it
+  static constexpr int NST = 4;
+  static constexpr int CODE_BYTES = BN * D;
+  static constexpr int RING_BYTES = NST * CODE_BYTES + NST * BN * 8 + NST * 8 + 16;
+  static constexpr int RING_OFF_FWD = ((TILES_FWD > MERGE_FWD ? TILES_FWD : MERGE_FWD) + 127) / 128 * 128;
+  static constexpr int RING_OFF_BWD = ((TILES_BWD > MERGE_BWD ? TILES_BWD : MERGE_BWD) + 127) / 128 * 128;
+  static constexpr int SMEM_FWD = RING_OFF_FWD + RING_BYTES;
+  static constexpr int SMEM_BWD = RING_OFF_BWD + RING_BYTES;
 };
 
 // 16 int8 codes -> 16 values (code - zp) * scale rounded to T, written as 32 bytes.
@@ -93,37 +103,84 @@ __device__ __forceinline__ void dequant16_store<__half>(uint8_t* dst, const uint
   *reinterpret_cast<uint4*>(dst + 16) = hi;
 }
 
-// Register-staged K/V tile: global codes (+ row scale / zero point) for the NEXT tile travel in registers
-// while the current tile is consumed.
+// K/V code tiles streamed through a shared-memory ring: one thread issues an untiled bulk copy per 64-token tile
+// (the rows of a head are contiguous), NST tiles ahead of the consumer; the per-key scale / zero point of a tile
+// travel through registers for one iteration and then into the ring's metadata slot.  commit() waits for the
+// tile's bytes (bounded wait) and dequantizes it into the padded 16-bit tile the MMAs read.
 template <int D, int MT>
-struct KvStager {
+struct KvRing {
   using C = SqCfg<D, MT>;
-  uint4 reg[C::CHUNKS];
-  float sc[C::CHUNKS], zp[C::CHUNKS];
+  uint8_t* codes;            // [NST][BN * D]
+  float2* meta;              // [NST][BN] (scale, zero point)
+  uint32_t bar0;             // NST mbarriers
+  volatile int* abort_flag;
+  const int8_t* src;
+  const uint16_t* scale;
+  const int8_t* zp;
+  int skv, n_tiles;
+  float2 pend;
+  int pend_slot;
 
-  __device__ __forceinline__ void prefetch(const ShortQDev& p, const int8_t* kvc, int64_t tok0, int n0, int tid) {
-#pragma unroll
-    for (int i = 0; i < C::CHUNKS; ++i) {
-      const int c = tid + i * C::THREADS;
-      const int r = c / C::CPR, cc = c % C::CPR;
-      const int n = n0 + r;
-      reg[i] = make_uint4(0, 0, 0, 0);
-      sc[i] = 0.f;
-      zp[i] = 0.f;
-      if (n < p.Skv) {
-        reg[i] = __ldg(reinterpret_cast<const uint4*>(kvc + n * p.kv.stride[2] + cc * 16));
-        sc[i] = half_bits_to_f32(p.kv.scale[tok0 + n]);
-        zp[i] = static_cast<float>(p.kv.zp[tok0 + n]);
-      }
+  __device__ __forceinline__ void issue(int tile) {
+    const int s = tile % C::NST;
+    const int rows = min(C::BN, skv - tile * C::BN);
+    const uint32_t bytes = static_cast<uint32_t>(rows) * D;
+    sm100::mbar_arrive_expect_tx(bar0 + 8 * s, bytes);
+    sm100::bulk_load_1d(smem_u32(codes + s * C::CODE_BYTES), src + static_cast<int64_t>(tile) * C::CODE_BYTES, bytes, bar0 + 8 * s);
+  }
+  __device__ __forceinline__ float2 load_meta(int tile, int tid) const {
+    const int n = tile * C::BN + tid;
+    return n < skv ? make_float2(half_bits_to_f32(scale[n]), static_cast<float>(zp[n])) : make_float2(0.f, 0.f);
+  }
+  // all threads; ends with the stages of the first NST tiles in flight.  The caller's next __syncthreads makes
+  // the metadata visible.
+  __device__ __forceinline__ void init(uint8_t* base, const ShortQDev& p, const int8_t* kvc, int64_t tok0, int tiles, int tid) {
+    codes = base;
+    meta = reinterpret_cast<float2*>(base + C::NST * C::CODE_BYTES);
+    uint8_t* bars = base + C::NST * C::CODE_BYTES + C::NST * C::BN * 8;
+    bar0 = smem_u32(bars);
+    abort_flag = reinterpret_cast<volatile int*>(bars + C::NST * 8);
+    src = kvc; scale = p.kv.scale + tok0; zp = p.kv.zp + tok0; skv = p.Skv; n_tiles = tiles;
+    pend_slot = -1;
+    if (tid == 0) {
+      *abort_flag = 0;
+      for (int s = 0; s < C::NST; ++s) sm100::mbar_init(bar0 + 8 * s, 1);
+      sm100::fence_barrier_init();
+    }
+    __syncthreads();
+    for (int tl = 0; tl < C::NST && tl < n_tiles; ++tl) {
+      if (tid == 0) issue(tl);
+      if (tid < C::BN) meta[tl * C::BN + tid] = load_meta(tl, tid);
     }
   }
+  // dequantize tile `tile` into sKV; false if the wait was abandoned
   template <typename T>
-  __device__ __forceinline__ void commit(uint8_t* sKV, int tid) const {
+  __device__ __forceinline__ bool commit(uint8_t* sKV, int tile, int tid) const {
+    const int s = tile % C::NST;
+    if (!sm100::mbar_wait(bar0 + 8 * s, (tile / C::NST) & 1, abort_flag, 0xffffffffu)) return false;
+    const uint8_t* cs = codes + s * C::CODE_BYTES;
+    const float2* ms = meta + s * C::BN;
 #pragma unroll
     for (int i = 0; i < C::CHUNKS; ++i) {
       const int c = tid + i * C::THREADS;
       const int r = c / C::CPR, cc = c % C::CPR;
-      dequant16_store<T>(sKV + r * C::T_STRIDE + cc * 32, reg[i], zp[i], sc[i]);
+      uint4 v = make_uint4(0, 0, 0, 0);
+      float2 m = make_float2(0.f, 0.f);
+      if (tile * C::BN + r < skv) {          // rows past the end were not copied: keep them zero
+        v = *reinterpret_cast<const uint4*>(cs + r * D + cc * 16);
+        m = ms[r];
+      }
+      dequant16_store<T>(sKV + r * C::T_STRIDE + cc * 32, v, m.y, m.x);
+    }
+    return true;
+  }
+  // after the __syncthreads that follows commit(tile): stage and metadata slot of `tile` are free again
+  __device__ __forceinline__ void refill(int tile, int tid) {
+    if (tid < C::BN && pend_slot >= 0) meta[pend_slot * C::BN + tid] = pend;     // loaded one iteration ago
+    pend_slot = -1;
+    if (tile + C::NST < n_tiles) {
+      if (tid == 0) issue(tile + C::NST);
+      if (tid < C::BN) { pend = load_meta(tile + C::NST, tid); pend_slot = tile % C::NST; }
     }
   }
 };
@@ -158,9 +215,9 @@ __global__ void __launch_bounds__(128) attn_fwd_shortq_kernel(ShortQDev p) {
       *reinterpret_cast<uint4*>(sQ + r * C::T_STRIDE + cc * 16) = v;
     }
   }
-  KvStager<D, MT> st;
+  KvRing<D, MT> st;
   const int n_tiles = (p.Skv + C::BN - 1) / C::BN;
-  st.prefetch(p, kvc, tok0, 0, tid);
+  st.init(smem + C::RING_OFF_FWD, p, kvc, tok0, n_tiles, tid);
   __syncthreads();
   // Q as MMA left operand, kept in registers for the whole walk (every warp works on all query rows)
   uint32_t qa[MT][D / 16][4];
@@ -181,13 +238,14 @@ __global__ void __launch_bounds__(128) attn_fwd_shortq_kernel(ShortQDev p) {
     for (int i = 0; i < D / 8; ++i) o_acc[mt][i][0] = o_acc[mt][i][1] = o_acc[mt][i][2] = o_acc[mt][i][3] = 0.f;
   }
   const int r0 = warp * 16;     // this warp's K/V rows inside the tile
+  bool failed = false;
 
   for (int tile = 0; tile < n_tiles; ++tile) {
     const int n0 = tile * C::BN;
     __syncthreads();
-    st.template commit<T>(sKV, tid);
-    __syncthreads();
-    if (tile + 1 < n_tiles) st.prefetch(p, kvc, tok0, n0 + C::BN, tid);
+    const bool arrived = st.template commit<T>(sKV, tile, tid);
+    if (!__syncthreads_and(arrived)) { failed = true; break; }
+    st.refill(tile, tid);
     if (n0 + r0 >= p.Skv) continue;       // this warp's 16 tokens are all past the end (warp-uniform)
 
     // S = Q K^T for 16 tokens: two 8-column MMA tiles
@@ -254,6 +312,10 @@ __global__ void __launch_bounds__(128) attn_fwd_shortq_kernel(ShortQDev p) {
     }
   }
 
+  if (failed) {
+    if (tid == 0 && p.status) *p.status = QFA_STATUS_WAIT_TIMEOUT;
+    return;
+  }
   // ---------------- merge the four warps' partial (m, l, O) and write O, LSE (quant_flash_attn.py:77-83)
   __syncthreads();
   float* sO = reinterpret_cast<float*>(smem);                          // [4][ROWS][D]
@@ -346,9 +408,10 @@ __global__ void __launch_bounds__(128) attn_bwd_shortq_kernel(ShortQDev p) {
         lse2[mt][nt][e] = ok ? p.lse_in[static_cast<int64_t>(bh) * p.lse_stride + qi] * kLog2e : INFINITY;
         dlt[mt][nt][e] = ok ? p.delta[static_cast<int64_t>(bh) * p.lse_stride + qi] : 0.f;
       }
-  KvStager<D, MT> st;
+  KvRing<D, MT> st;
   const int n_tiles = (p.Skv + C::BN - 1) / C::BN;
-  st.prefetch(p, kvc, tok0, 0, tid);
+  st.init(smem + C::RING_OFF_BWD, p, kvc, tok0, n_tiles, tid);
+  bool failed = false;
 
   float dq_acc[MT][D / 8][4];
 #pragma unroll
@@ -362,9 +425,9 @@ __global__ void __launch_bounds__(128) attn_bwd_shortq_kernel(ShortQDev p) {
   for (int tile = 0; tile < n_tiles; ++tile) {
     const int n0 = tile * C::BN;
     __syncthreads();
-    st.template commit<T>(sKV, tid);
-    __syncthreads();
-    if (tile + 1 < n_tiles) st.prefetch(p, kvc, tok0, n0 + C::BN, tid);
+    const bool arrived = st.template commit<T>(sKV, tile, tid);
+    if (!__syncthreads_and(arrived)) { failed = true; break; }
+    st.refill(tile, tid);
     if (n0 + r0 >= p.Skv) continue;       // warp-uniform
 
     // left operand K^ = V^ rows of this warp; right operands Q and dO as (n = query, k = d)
@@ -474,6 +537,10 @@ __global__ void __launch_bounds__(128) attn_bwd_shortq_kernel(ShortQDev p) {
     }
   }
 
+  if (failed) {
+    if (tid == 0 && p.status) *p.status = QFA_STATUS_WAIT_TIMEOUT;
+    return;
+  }
   // ---------------- dQ = sm_scale * sum over the four warps (quant_flash_attn.py:164-166)
   __syncthreads();
   float* sD = reinterpret_cast<float*>(smem);      // [4][ROWS][D]
@@ -547,13 +614,17 @@ static bool same_tensor(const QfaQuantTensor& a, const QfaQuantTensor& b) {
          a.stride[1] == b.stride[1] && a.stride[2] == b.stride[2];
 }
 
+// the code tiles travel as untiled bulk copies: the rows of a head must be contiguous and 16-byte aligned
+static bool bulk_copyable(const QfaQuantTensor& t, int64_t D) {
+  return t.stride[2] == D && (reinterpret_cast<uintptr_t>(t.codes) & 15) == 0 && t.stride[0] % 16 == 0 && t.stride[1] % 16 == 0;
+}
 int attn_fwd_shortq_supported(const QfaFwdArgs& a) {
   return a.mode == QFA_MODE_REF && !a.causal && a.Sq <= 32 && same_tensor(a.k, a.v) && (a.D == 64 || a.D == 128) &&
-         a.B * a.H <= 0x7fffffffLL;
+         a.B * a.H <= 0x7fffffffLL && bulk_copyable(a.k, a.D);
 }
 int attn_bwd_shortq_supported(const QfaBwdArgs& a) {
   return a.mode == QFA_MODE_REF && !a.causal && a.dkv_fused && a.Sq <= 32 && same_tensor(a.k, a.v) &&
-         (a.D == 64 || a.D == 128) && a.B * a.H <= 0x7fffffffLL;
+         (a.D == 64 || a.D == 128) && a.B * a.H <= 0x7fffffffLL && bulk_copyable(a.k, a.D);
 }
 
 #define QFA_SQ_DISPATCH(FN, dev, heads, stream)                                                            \
@@ -573,6 +644,7 @@ int attn_fwd_shortq_entry(const QfaFwdArgs& a, cudaStream_t stream) {
   for (int i = 0; i < 3; ++i) { d.q_stride[i] = a.q_stride[i]; d.o_stride[i] = a.o_stride[i]; }
   d.kv = a.k; d.o = a.o; d.lse = a.lse; d.lse_stride = a.lse_stride;
   d.H = static_cast<int>(a.H); d.Sq = static_cast<int>(a.Sq); d.Skv = static_cast<int>(a.Skv); d.sm_scale = a.sm_scale;
+  d.status = a.status;
   const int dtype = a.dtype, mt = a.Sq <= 16 ? 1 : 2;
   const int64_t D = a.D, heads = a.B * a.H;
   QFA_SQ_DISPATCH(launch_fwd_sq, d, heads, stream);
@@ -588,6 +660,7 @@ int attn_bwd_shortq_entry(const QfaBwdArgs& a, cudaStream_t stream) {
   d.kv = a.k; d.d_o = a.d_o; d.lse_in = a.lse; d.delta = a.delta; d.lse_stride = a.lse_stride;
   d.dq = a.dq; d.dkv = a.dk;
   d.H = static_cast<int>(a.H); d.Sq = static_cast<int>(a.Sq); d.Skv = static_cast<int>(a.Skv); d.sm_scale = a.sm_scale;
+  d.status = a.status;
   const int dtype = a.dtype, mt = a.Sq <= 16 ? 1 : 2;
   const int64_t D = a.D, heads = a.B * a.H;
   QFA_SQ_DISPATCH(launch_bwd_sq, d, heads, stream);
