@@ -5,6 +5,7 @@ Public entry points (same names and conventions as the reference project's modul
     asymmetric_quant_per_token(x)                      -> (codes, scale, zero_point)
     quant_flash_attn(q, kv_fp16, kv_quant, sm_scale)   -> o        (autograd: dq, dkv)
     quant_attention(q, k, v, causal, sm_scale)         -> o        (autograd: dq, dk, dv)
+    quant_attention_host(q, k, v, causal, sm_scale)    -> o        (host tensors in and out, copies overlapped)
 
 All of them require a CUDA device and the in-tree shared library libqfa_sm100a.so.
 """
@@ -14,6 +15,7 @@ from .asymmetric_quant import (  # noqa: F401
 from .quant_flash_attn import (  # noqa: F401
     QuantFlashAttention, quant_flash_attn, QuantAttention, quant_attention,
     quantize_qkv, int8_attention_forward, int8_attention_backward, dequantize_16bit,
+    HostAttentionPipeline, quant_attention_host,
 )
 from .sharding import head_slice, shard_bounds  # noqa: F401
 from ._lib import launch_count  # noqa: F401
@@ -22,5 +24,6 @@ __all__ = [
     "asymmetric_quant_per_token", "asymmetric_quant_per_token_ex", "dequantize_per_token",
     "QuantFlashAttention", "quant_flash_attn", "QuantAttention", "quant_attention",
     "quantize_qkv", "int8_attention_forward", "int8_attention_backward", "dequantize_16bit",
+    "HostAttentionPipeline", "quant_attention_host",
     "head_slice", "shard_bounds", "launch_count",
 ]

@@ -259,3 +259,99 @@ class QuantAttention(torch.autograd.Function):
 
 
 quant_attention = QuantAttention.apply
+
+
+class HostAttentionPipeline:
+    """Inference-time int8 attention for operands that live in HOST memory.
+
+    Heads are independent units of the path, so the (batch x head) axis is cut into slices that move through
+    three CUDA streams: while slice i is quantized and attended to, slice i+1 is on its way to the device and
+    the output of slice i-1 on its way back.  The host <-> device link carries 3 input bytes for every output
+    byte, so with the copies overlapped a call costs about as much as the input copy alone.
+
+    Device buffers for two slices in flight are allocated once per (shape, dtype) and reused.  Host tensors
+    should be pinned; pageable memory works but the copies then serialize on the host.
+    """
+
+    def __init__(self, device=None, slices: int = 16):
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.slices = int(slices)
+        with torch.cuda.device(self.device):
+            self.s_in, self.s_run, self.s_out = (torch.cuda.Stream() for _ in range(3))
+        self._key = None
+        self._bufs = None
+
+    def _buffers(self, heads, Sq, Skv, D, dtype):
+        key = (heads, Sq, Skv, D, dtype)
+        if key != self._key:
+            mk = lambda S: torch.empty((1, heads, S, D), dtype=dtype, device=self.device)
+            self._bufs = [(mk(Sq), mk(Skv), mk(Skv)) for _ in range(2)]
+            self._key = key
+        return self._bufs
+
+    def __call__(self, q, k, v, causal=False, sm_scale=None, out=None):
+        """q (B,H,Sq,D), k, v (B,H,Skv,D): contiguous host tensors, fp16 or bf16.  Returns `out` (host, pinned
+        if it is allocated here) after everything has landed in it."""
+        for name, t in (("q", q), ("k", k), ("v", v)):
+            if t.is_cuda or not t.is_contiguous() or t.dim() != 4 or t.dtype != q.dtype or t.dtype not in _DT:
+                raise ValueError(f"{name}: expected a contiguous 4-D host tensor, float16 or bfloat16")
+        B, H, Sq, D = q.shape
+        Skv = k.shape[2]
+        if k.shape != v.shape or k.shape[:2] != (B, H) or k.shape[3] != D:
+            raise ValueError("expected q (B,H,Sq,D) and k, v (B,H,Skv,D)")
+        _check_head_dim(D)
+        sm_scale = 1.0 / (D ** 0.5) if sm_scale is None else float(sm_scale)
+        if out is None:
+            out = torch.empty(q.shape, dtype=q.dtype).pin_memory()
+        n = B * H
+        per = -(-n // max(1, min(self.slices, n)))
+        qf, kf, vf, of = (t.view(1, n, t.shape[2], D) for t in (q, k, v, out))
+        bufs = self._buffers(per, Sq, Skv, D, q.dtype)
+        free = [None, None]          # event after which a buffer set may be overwritten
+        keep = []
+        with torch.cuda.device(self.device):
+            start = torch.cuda.Event()
+            start.record(torch.cuda.current_stream())
+            for s_ in (self.s_in, self.s_run, self.s_out):
+                s_.wait_event(start)
+            for i, h0 in enumerate(range(0, n, per)):
+                h1 = min(n, h0 + per)
+                dq, dk, dv = (b[:, : h1 - h0] for b in bufs[i & 1])
+                if free[i & 1] is not None:
+                    self.s_in.wait_event(free[i & 1])
+                with torch.cuda.stream(self.s_in):
+                    dq.copy_(qf[:, h0:h1], non_blocking=True)
+                    dk.copy_(kf[:, h0:h1], non_blocking=True)
+                    dv.copy_(vf[:, h0:h1], non_blocking=True)
+                    landed = torch.cuda.Event()
+                    landed.record(self.s_in)
+                self.s_run.wait_event(landed)
+                with torch.cuda.stream(self.s_run):
+                    qq, kq, vq = quantize_qkv(dq, dk, dv)
+                    o, _ = int8_attention_forward(qq, kq, vq, causal, sm_scale, q.dtype)
+                    done = torch.cuda.Event()
+                    done.record(self.s_run)
+                free[i & 1] = done
+                self.s_out.wait_event(done)
+                with torch.cuda.stream(self.s_out):
+                    of[:, h0:h1].copy_(o, non_blocking=True)
+                o.record_stream(self.s_out)
+                keep.append((qq, kq, vq, o))
+            finish = torch.cuda.Event()
+            finish.record(self.s_out)
+            torch.cuda.current_stream().wait_event(finish)
+            finish.synchronize()
+        return out
+
+
+_host_pipelines = {}
+
+
+def quant_attention_host(q, k, v, causal=False, sm_scale=None, out=None, device=None, slices: int = 16):
+    """`quant_attention` (forward only) for host-resident q, k, v; see HostAttentionPipeline."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = (dev, int(slices))
+    if key not in _host_pipelines:
+        _host_pipelines[key] = HostAttentionPipeline(dev, slices)
+    return _host_pipelines[key](q, k, v, causal, sm_scale, out)
+

@@ -207,6 +207,21 @@ def test_int8_mode_growing_logits(qfa, dtype, causal, slope):
     _close(o, o_ref, rel=REL_TOL + HALF_ULP[dtype], what="o")
 
 
+@pytest.mark.parametrize("causal", [False, True])
+def test_host_pipeline_matches_device_operator(qfa, causal):
+    """quant_attention_host (heads sliced over three streams, host tensors in and out) returns exactly what
+    quant_attention returns for the same operands; 7 heads over 3 slices leaves a ragged last slice."""
+    B, H, S, D = 1, 7, 200, 128
+    q, k, v = (_gen((B, H, S, D), torch.bfloat16, s) for s in (41, 42, 43))
+    sm = 1.0 / math.sqrt(D)
+    want = qfa.quant_attention(q.cuda(), k.cuda(), v.cuda(), causal, sm).cpu()
+    got = qfa.quant_attention_host(q.pin_memory(), k.pin_memory(), v.pin_memory(), causal, sm, slices=3)
+    assert not got.is_cuda and torch.equal(got, want)
+    # a second call reuses the pipeline's buffers
+    got2 = qfa.quant_attention_host(q.pin_memory(), k.pin_memory(), v.pin_memory(), causal, sm, slices=3)
+    assert torch.equal(got2, want)
+
+
 def test_training_shape_properties(qfa):
     """BASELINE config 3 (B8 H16 S2048 D64 causal) at full size: the oracle is too slow there, so
     check size-independent properties: finite outputs, row 0 attends only to token 0, gradient
