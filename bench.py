@@ -53,15 +53,53 @@ def make_inputs(b, h, s, d, device, seed_base, head0=0, dtype=torch.bfloat16):
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed region runs: NVML read-only queries from a thread
+    (a few milliseconds apart, so that even a short timed region gets samples), or an `nvidia-smi -lms` child
+    process if the NVML binding is missing."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
         self.index, self.lines, self.proc = index, [], None
+        self.samples, self._stop, self._thread, self._nvml = [], False, None, None
+
+    def _nvml_handle(self):
+        import pynvml
+        pynvml.nvmlInit()
+        self._nvml = pynvml
+        try:
+            uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+            return pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+        except Exception:
+            return pynvml.nvmlDeviceGetHandleByIndex(self.index)
+
+    def _poll(self, handle):
+        n = self._nvml
+        # NVML clocks-event-reason bits
+        bits = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
+        try:
+            mx = n.nvmlDeviceGetMaxClockInfo(handle, n.NVML_CLOCK_SM)
+        except Exception:
+            mx = None
+        get_reasons = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or n.nvmlDeviceGetCurrentClocksThrottleReasons
+        while not self._stop:
+            try:
+                sm = n.nvmlDeviceGetClockInfo(handle, n.NVML_CLOCK_SM)
+                r = get_reasons(handle)
+                self.samples.append((time.time(), float(sm), mx, [k for k, b in bits.items() if r & b]))
+            except Exception:
+                pass
+            time.sleep(0.004)
 
     def start(self):
+        try:
+            handle = self._nvml_handle()
+            self._thread = threading.Thread(target=self._poll, args=(handle,), daemon=True)
+            self._thread.start()
+            return
+        except Exception:
+            self._thread = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "20",
@@ -76,10 +114,20 @@ class ClockSampler:
 
     def window(self, t0, t1):
         """Keep only the samples taken inside [t0, t1] (the timed region)."""
+        inside = [x for x in self.samples if t0 <= x[0] <= t1]
+        self.samples = inside if inside else self.samples[-3:]
         inside = [x for x in self.lines if t0 <= x[0] <= t1]
         self.lines = inside if inside else self.lines[-3:]
 
     def stop(self):
+        if self._thread is not None:
+            self._stop = True
+            self._thread.join(timeout=1.0)
+            sm = sorted(x[1] for x in self.samples)
+            mx = [x[2] for x in self.samples if x[2]]
+            reasons = sorted({r for x in self.samples for r in x[3]})
+            return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": float(max(mx)) if mx else None,
+                    "reasons": reasons, "samples": len(sm), "source": "nvml"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -97,7 +145,7 @@ class ClockSampler:
                     reasons.add(name)
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "source": "nvidia-smi"}
 
 
 def load_peaks():
