@@ -61,13 +61,14 @@ struct SqCfg {
   static constexpr int MERGE_BWD = 4 * ROWS * D * 4;
   // ring of raw code tiles filled by bulk copies + (scale, zero point) per key + one mbarrier per stage; it sits
   // behind the larger of the tile / merge regions so that the final merge never overlaps it
-  static constexpr int NST = 4;
+  // (the forward keeps four tiles in flight with three CTAs per SM; the backward two tiles with four CTAs per SM)
+  static constexpr int NST_FWD = 4, NST_BWD = 2;
   static constexpr int CODE_BYTES = BN * D;
-  static constexpr int RING_BYTES = NST * CODE_BYTES + NST * BN * 8 + NST * 8 + 16;
+  static constexpr int ring_bytes(int nst) { return nst * CODE_BYTES + nst * BN * 8 + nst * 8 + 16; }
   static constexpr int RING_OFF_FWD = ((TILES_FWD > MERGE_FWD ? TILES_FWD : MERGE_FWD) + 127) / 128 * 128;
   static constexpr int RING_OFF_BWD = ((TILES_BWD > MERGE_BWD ? TILES_BWD : MERGE_BWD) + 127) / 128 * 128;
-  static constexpr int SMEM_FWD = RING_OFF_FWD + RING_BYTES;
-  static constexpr int SMEM_BWD = RING_OFF_BWD + RING_BYTES;
+  static constexpr int SMEM_FWD = RING_OFF_FWD + ring_bytes(NST_FWD);
+  static constexpr int SMEM_BWD = RING_OFF_BWD + ring_bytes(NST_BWD);
 };
 
 // 16 int8 codes -> 16 values (code - zp) * scale rounded to T, written as 32 bytes.
@@ -107,7 +108,7 @@ __device__ __forceinline__ void dequant16_store<__half>(uint8_t* dst, const uint
 // (the rows of a head are contiguous), NST tiles ahead of the consumer; the per-key scale / zero point of a tile
 // travel through registers for one iteration and then into the ring's metadata slot.  commit() waits for the
 // tile's bytes (bounded wait) and dequantizes it into the padded 16-bit tile the MMAs read.
-template <int D, int MT>
+template <int D, int MT, int NST>
 struct KvRing {
   using C = SqCfg<D, MT>;
   uint8_t* codes;            // [NST][BN * D]
@@ -122,7 +123,7 @@ struct KvRing {
   int pend_slot;
 
   __device__ __forceinline__ void issue(int tile) {
-    const int s = tile % C::NST;
+    const int s = tile % NST;
     const int rows = min(C::BN, skv - tile * C::BN);
     const uint32_t bytes = static_cast<uint32_t>(rows) * D;
     sm100::mbar_arrive_expect_tx(bar0 + 8 * s, bytes);
@@ -136,19 +137,19 @@ struct KvRing {
   // the metadata visible.
   __device__ __forceinline__ void init(uint8_t* base, const ShortQDev& p, const int8_t* kvc, int64_t tok0, int tiles, int tid) {
     codes = base;
-    meta = reinterpret_cast<float2*>(base + C::NST * C::CODE_BYTES);
-    uint8_t* bars = base + C::NST * C::CODE_BYTES + C::NST * C::BN * 8;
+    meta = reinterpret_cast<float2*>(base + NST * C::CODE_BYTES);
+    uint8_t* bars = base + NST * C::CODE_BYTES + NST * C::BN * 8;
     bar0 = smem_u32(bars);
-    abort_flag = reinterpret_cast<volatile int*>(bars + C::NST * 8);
+    abort_flag = reinterpret_cast<volatile int*>(bars + NST * 8);
     src = kvc; scale = p.kv.scale + tok0; zp = p.kv.zp + tok0; skv = p.Skv; n_tiles = tiles;
     pend_slot = -1;
     if (tid == 0) {
       *abort_flag = 0;
-      for (int s = 0; s < C::NST; ++s) sm100::mbar_init(bar0 + 8 * s, 1);
+      for (int s = 0; s < NST; ++s) sm100::mbar_init(bar0 + 8 * s, 1);
       sm100::fence_barrier_init();
     }
     __syncthreads();
-    for (int tl = 0; tl < C::NST && tl < n_tiles; ++tl) {
+    for (int tl = 0; tl < NST && tl < n_tiles; ++tl) {
       if (tid == 0) issue(tl);
       if (tid < C::BN) meta[tl * C::BN + tid] = load_meta(tl, tid);
     }
@@ -156,8 +157,8 @@ struct KvRing {
   // dequantize tile `tile` into sKV; false if the wait was abandoned
   template <typename T>
   __device__ __forceinline__ bool commit(uint8_t* sKV, int tile, int tid) const {
-    const int s = tile % C::NST;
-    if (!sm100::mbar_wait(bar0 + 8 * s, (tile / C::NST) & 1, abort_flag, 0xffffffffu)) return false;
+    const int s = tile % NST;
+    if (!sm100::mbar_wait(bar0 + 8 * s, (tile / NST) & 1, abort_flag, 0xffffffffu)) return false;
     const uint8_t* cs = codes + s * C::CODE_BYTES;
     const float2* ms = meta + s * C::BN;
 #pragma unroll
@@ -178,9 +179,9 @@ struct KvRing {
   __device__ __forceinline__ void refill(int tile, int tid) {
     if (tid < C::BN && pend_slot >= 0) meta[pend_slot * C::BN + tid] = pend;     // loaded one iteration ago
     pend_slot = -1;
-    if (tile + C::NST < n_tiles) {
-      if (tid == 0) issue(tile + C::NST);
-      if (tid < C::BN) { pend = load_meta(tile + C::NST, tid); pend_slot = tile % C::NST; }
+    if (tile + NST < n_tiles) {
+      if (tid == 0) issue(tile + NST);
+      if (tid < C::BN) { pend = load_meta(tile + NST, tid); pend_slot = tile % NST; }
     }
   }
 };
@@ -215,7 +216,7 @@ __global__ void __launch_bounds__(128) attn_fwd_shortq_kernel(ShortQDev p) {
       *reinterpret_cast<uint4*>(sQ + r * C::T_STRIDE + cc * 16) = v;
     }
   }
-  KvRing<D, MT> st;
+  KvRing<D, MT, C::NST_FWD> st;
   const int n_tiles = (p.Skv + C::BN - 1) / C::BN;
   st.init(smem + C::RING_OFF_FWD, p, kvc, tok0, n_tiles, tid);
   __syncthreads();
@@ -367,7 +368,7 @@ __global__ void __launch_bounds__(128) attn_fwd_shortq_kernel(ShortQDev p) {
 // Per 64-token tile and warp (16 tokens): S^T = K^ Q^T, P^T = exp(S^T*sm - LSE), dP^T = V^ dO^T,
 // dS^T = P^T*(dP^T - delta), dKV rows = P^T dO + sm * dS^T Q  (written once), dQ += dS K^ (registers).
 template <typename T, int D, int MT>
-__global__ void __launch_bounds__(128) attn_bwd_shortq_kernel(ShortQDev p) {
+__global__ void __launch_bounds__(128, MT == 1 ? 4 : 1) attn_bwd_shortq_kernel(ShortQDev p) {
   using C = SqCfg<D, MT>;
   using H16 = Half16<T>;
   extern __shared__ __align__(16) uint8_t smem[];
@@ -408,7 +409,7 @@ __global__ void __launch_bounds__(128) attn_bwd_shortq_kernel(ShortQDev p) {
         lse2[mt][nt][e] = ok ? p.lse_in[static_cast<int64_t>(bh) * p.lse_stride + qi] * kLog2e : INFINITY;
         dlt[mt][nt][e] = ok ? p.delta[static_cast<int64_t>(bh) * p.lse_stride + qi] : 0.f;
       }
-  KvRing<D, MT> st;
+  KvRing<D, MT, C::NST_BWD> st;
   const int n_tiles = (p.Skv + C::BN - 1) / C::BN;
   st.init(smem + C::RING_OFF_BWD, p, kvc, tok0, n_tiles, tid);
   bool failed = false;
@@ -479,41 +480,44 @@ __global__ void __launch_bounds__(128) attn_bwd_shortq_kernel(ShortQDev p) {
         *reinterpret_cast<uint32_t*>(sDS + (r0 + g + 8) * C::DS_STRIDE + (mt * 16 + nt * 8 + 2 * t) * 2) =
             H16::pack(dp_[mt][nt][2], dp_[mt][nt][3]);
       }
-    // dKV rows of this warp = P^T dO + sm * dS^T Q  (k = queries)
+    // dKV rows of this warp = P^T dO + sm * dS^T Q  (k = queries).  One 16-column group of D at a time, written
+    // out at once: the accumulator of the whole row (D/8 x 4 registers) would cost a resident CTA per SM
     {
-      float acc[D / 8][4];
-#pragma unroll
-      for (int i = 0; i < D / 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
       const uint32_t bdo_t = smem_u32(sDO + ((lane & 7) + ((lane >> 3) & 1) * 8) * C::T_STRIDE + ((lane >> 4) & 1) * 16);
       const uint32_t bq_t = smem_u32(sQ + ((lane & 7) + ((lane >> 3) & 1) * 8) * C::T_STRIDE + ((lane >> 4) & 1) * 16);
+      uint32_t ap[MT][4], ads[MT][4];
+      // sm_scale * dS^T as the left operand of the dK product, so that dV and sm*dK share one accumulator
+      const float sm = p.sm_scale;
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
-        uint32_t ap[4], ads[4];
-        ap[0] = H16::pack(st_[mt][0][0], st_[mt][0][1]); ap[1] = H16::pack(st_[mt][0][2], st_[mt][0][3]);
-        ap[2] = H16::pack(st_[mt][1][0], st_[mt][1][1]); ap[3] = H16::pack(st_[mt][1][2], st_[mt][1][3]);
-        // sm_scale * dS^T as the left operand of the dK product, so that dV and sm*dK share one accumulator
-        const float sm = p.sm_scale;
-        ads[0] = H16::pack(sm * dp_[mt][0][0], sm * dp_[mt][0][1]); ads[1] = H16::pack(sm * dp_[mt][0][2], sm * dp_[mt][0][3]);
-        ads[2] = H16::pack(sm * dp_[mt][1][0], sm * dp_[mt][1][1]); ads[3] = H16::pack(sm * dp_[mt][1][2], sm * dp_[mt][1][3]);
+        ap[mt][0] = H16::pack(st_[mt][0][0], st_[mt][0][1]); ap[mt][1] = H16::pack(st_[mt][0][2], st_[mt][0][3]);
+        ap[mt][2] = H16::pack(st_[mt][1][0], st_[mt][1][1]); ap[mt][3] = H16::pack(st_[mt][1][2], st_[mt][1][3]);
+        ads[mt][0] = H16::pack(sm * dp_[mt][0][0], sm * dp_[mt][0][1]); ads[mt][1] = H16::pack(sm * dp_[mt][0][2], sm * dp_[mt][0][3]);
+        ads[mt][2] = H16::pack(sm * dp_[mt][1][0], sm * dp_[mt][1][1]); ads[mt][3] = H16::pack(sm * dp_[mt][1][2], sm * dp_[mt][1][3]);
+      }
+      const int n_lo = n0 + r0 + g, n_hi = n_lo + 8;
+      T* row_lo = dkv + static_cast<int64_t>(n_lo) * p.dkv_stride[2] + 2 * t;
+      T* row_hi = dkv + static_cast<int64_t>(n_hi) * p.dkv_stride[2] + 2 * t;
 #pragma unroll
-        for (int dpp = 0; dpp < D / 16; ++dpp) {
+      for (int dpp = 0; dpp < D / 16; ++dpp) {
+        float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
           uint32_t b0, b1, b2, b3;
           ldsm_x4_t(bdo_t + mt * 16 * C::T_STRIDE + dpp * 32, b0, b1, b2, b3);
-          mma_16816<T>(acc[2 * dpp], ap, b0, b1);
-          mma_16816<T>(acc[2 * dpp + 1], ap, b2, b3);
+          mma_16816<T>(acc[0], ap[mt], b0, b1);
+          mma_16816<T>(acc[1], ap[mt], b2, b3);
           ldsm_x4_t(bq_t + mt * 16 * C::T_STRIDE + dpp * 32, b0, b1, b2, b3);
-          mma_16816<T>(acc[2 * dpp], ads, b0, b1);
-          mma_16816<T>(acc[2 * dpp + 1], ads, b2, b3);
+          mma_16816<T>(acc[0], ads[mt], b0, b1);
+          mma_16816<T>(acc[1], ads[mt], b2, b3);
         }
-      }
-#pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        const int n = n0 + r0 + g + 8 * r;
-        if (n < p.Skv) {
-#pragma unroll
-          for (int i = 0; i < D / 8; ++i)
-            *reinterpret_cast<uint32_t*>(dkv + n * p.dkv_stride[2] + i * 8 + 2 * t) =
-                H16::pack(acc[i][2 * r], acc[i][2 * r + 1]);
+        if (n_lo < p.Skv) {
+          *reinterpret_cast<uint32_t*>(row_lo + dpp * 16) = H16::pack(acc[0][0], acc[0][1]);
+          *reinterpret_cast<uint32_t*>(row_lo + dpp * 16 + 8) = H16::pack(acc[1][0], acc[1][1]);
+        }
+        if (n_hi < p.Skv) {
+          *reinterpret_cast<uint32_t*>(row_hi + dpp * 16) = H16::pack(acc[0][2], acc[0][3]);
+          *reinterpret_cast<uint32_t*>(row_hi + dpp * 16 + 8) = H16::pack(acc[1][2], acc[1][3]);
         }
       }
     }
