@@ -310,6 +310,12 @@ def run_ours(args):
             extra["fwd_bwd_B4H32S4096D128_" + ("causal" if causal else "noncausal")] = {
                 "fwd_ms": f_ms, "bwd_ms": b_ms, "bwd_TOPS": 2.5 * fo / b_ms / 1e9, "TOPS": 3.5 * fo / (f_ms + b_ms) / 1e9}
         del hdo, ho, hlse
+        # flash_attn_func-style front end: the same workload handed over in (B,S,H,D) memory; quantization and
+        # attention read and write through strides, so this should cost what the timed step costs
+        fq, fk, fv = (t.transpose(1, 2).contiguous() for t in (q, k, v))
+        fe_ms = time_ms(lambda: qfa.quant_flash_attn_func(fq, fk, fv, causal=False, softmax_scale=sm), reps=5)
+        extra["frontend_bshd_B4S4096H32D128"] = {"ms": fe_ms, "TOPS": ops_step / fe_ms / 1e9}
+        del fq, fk, fv
         # training shape: B8 H16 S2048 D64 causal, forward + backward (ops = 3.5 x forward)
         tb, th, ts, td = 8, 16, 2048, 64
         tq, tk, tv = make_inputs(tb, th, ts, td, dev, seed_base=99)

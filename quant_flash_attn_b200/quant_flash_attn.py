@@ -244,7 +244,9 @@ class QuantAttention(torch.autograd.Function):
         if k.shape != v.shape or q.shape[:2] != k.shape[:2] or q.shape[3] != k.shape[3]:
             raise ValueError("expected q (B,H,Sq,D) and k, v (B,H,Skv,D)")
         qq, kq, vq = quantize_qkv(q, k, v)
-        o, lse = int8_attention_forward(qq, kq, vq, causal, sm_scale, q.dtype)
+        # the output takes q's memory layout (the kernels write through strides), so a (B,S,H,D) caller that
+        # passes transposed views gets its result in (B,S,H,D) memory without a copy
+        o, lse = int8_attention_forward(qq, kq, vq, causal, sm_scale, q.dtype, o=torch.empty_like(q))
         ctx.save_for_backward(o, lse, *qq[:4], *kq[:4], *vq[:3], vq[4])
         ctx.causal, ctx.sm_scale = bool(causal), float(sm_scale)
         return o
