@@ -22,7 +22,7 @@ from .quant_flash_attn import (  # noqa: F401
 from .flash_attn_interface import (  # noqa: F401
     quant_flash_attn_func, quant_flash_attn_kvpacked_func, quant_flash_attn_varlen_func,
 )
-from .sharding import head_slice, shard_bounds  # noqa: F401
+from .sharding import all_gather_heads, head_slice, shard_bounds  # noqa: F401
 from ._lib import launch_count  # noqa: F401
 
 __all__ = [
@@ -31,5 +31,5 @@ __all__ = [
     "quantize_qkv", "int8_attention_forward", "int8_attention_backward", "dequantize_16bit",
     "HostAttentionPipeline", "quant_attention_host",
     "quant_flash_attn_func", "quant_flash_attn_kvpacked_func", "quant_flash_attn_varlen_func",
-    "head_slice", "shard_bounds", "launch_count",
+    "all_gather_heads", "head_slice", "shard_bounds", "launch_count",
 ]

@@ -3,7 +3,9 @@
 The attention kernels' unit of work is one (batch, head) pair (the reference's grid unit,
 quant_flash_attn.py:187) and the quantizer's is one token row (asymmetric_quant.py:132); units are
 independent, so multi-GPU runs give every rank a contiguous, equal slice of the flattened B*H
-axis and need no collective on the data path.
+axis and need no collective on the data path.  `all_gather_heads` is the one step AFTER the path that
+needs the interconnect: when the heads of all ranks belong to one model layer, the layer's next
+operator wants the whole (B,H,S,D) output on every rank.
 """
 from __future__ import annotations
 
@@ -24,3 +26,32 @@ def head_slice(t, world_size: int, rank: int):
     B, H = t.shape[0], t.shape[1]
     s, e = shard_bounds(B * H, world_size, rank)
     return t.reshape(1, B * H, *t.shape[2:])[:, s:e]
+
+
+def all_gather_heads(local, batch: int, heads: int, group=None):
+    """Inverse of `head_slice` across a process group: every rank passes its (1, n_local, S, D) slice
+    (n_local from `shard_bounds`) and receives the full (batch, heads, S, D) tensor.
+
+    One `all_gather` over the group's backend (NCCL rides NVLink / NVSwitch between the GPUs of a node;
+    gloo on CPU).  Slices may differ by one head between ranks, so the shorter ones are padded to the
+    longest for the collective and trimmed afterwards.  Not part of the attention path: heads never
+    exchange data while they are computed."""
+    import torch
+    import torch.distributed as dist
+
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    n = batch * heads
+    spans = [shard_bounds(n, world, r) for r in range(world)]
+    s, e = spans[rank]
+    if local.shape[0] != 1 or local.shape[1] != e - s:
+        raise ValueError(f"rank {rank} holds heads [{s}, {e}) but passed a tensor of shape {tuple(local.shape)}")
+    longest = max(b - a for a, b in spans)
+    send = local.contiguous()
+    if e - s < longest:
+        pad = torch.zeros((1, longest - (e - s), *local.shape[2:]), dtype=local.dtype, device=local.device)
+        send = torch.cat([send, pad], dim=1)
+    recv = [torch.empty_like(send) for _ in range(world)]
+    dist.all_gather(recv, send, group=group)
+    full = torch.cat([recv[r][:, : spans[r][1] - spans[r][0]] for r in range(world)], dim=1)
+    return full.reshape(batch, heads, *local.shape[2:])
+

@@ -33,7 +33,15 @@ def _worker(rank, world, port, out_dir):
     dist.barrier()
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     assert t.item() == world
-    torch.save({"span": (s, e), "o": o, "lse": lse}, os.path.join(out_dir, f"r{rank}.pt"))
+    # after the path: one all-gather puts the whole layer output on every rank (5 heads over 2 ranks would be
+    # uneven; here 6 heads split 3 + 3, the uneven case runs below with world size 3 worth of bounds)
+    from quant_flash_attn_b200 import all_gather_heads
+    full = all_gather_heads(o, B, H)
+    assert full.shape == (B, H, S, D) and torch.equal(full.reshape(1, B * H, S, D)[:, s:e], o)
+    uneven = torch.full((1, shard_bounds(5, world, rank)[1] - shard_bounds(5, world, rank)[0], 4, 8), float(rank))
+    got = all_gather_heads(uneven, 1, 5)
+    assert got.shape == (1, 5, 4, 8) and got[0, :3].eq(0).all() and got[0, 3:].eq(1).all()
+    torch.save({"span": (s, e), "o": o, "lse": lse, "gathered": full}, os.path.join(out_dir, f"r{rank}.pt"))
     dist.destroy_process_group()
 
 
@@ -50,3 +58,5 @@ def test_two_rank_head_partition_matches_single_process(tmp_path):
     o = torch.cat([p["o"] for p in parts], dim=1).reshape(B, H, S, D)
     lse = torch.cat([p["lse"] for p in parts], dim=1).reshape(B, H, S)
     assert torch.equal(o, o_full) and torch.equal(lse, lse_full)
+    for part in parts:
+        assert torch.equal(part["gathered"], o_full)
