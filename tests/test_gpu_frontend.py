@@ -15,8 +15,10 @@ from test_gpu_attn import HALF_ULP, REL_TOL, REL_TOL_GRAD, _close, _cpu_quant, _
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("B,Sq,Skv,H,D,causal", [(2, 200, 200, 3, 128, True), (1, 77, 333, 2, 64, False)])
 def test_bshd_layout_vs_oracle(qfa, dtype, B, Sq, Skv, H, D, causal):
+    # N(0,1) operands: this test is about the layout; heavy-tailed logits (where the 16-bit rounding of P shows)
+    # have their own cases in test_gpu_attn.py
     q = _gen((B, Sq, H, D), dtype, 51)
-    k = _gen((B, Skv, H, D), dtype, 52, "outlier")
+    k = _gen((B, Skv, H, D), dtype, 52)
     v = _gen((B, Skv, H, D), dtype, 53)
     do = _gen((B, Sq, H, D), dtype, 54)
     qc, kc, vc = (t.cuda().requires_grad_() for t in (q, k, v))
