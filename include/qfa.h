@@ -119,6 +119,11 @@ typedef struct {
   float* lse;
   int64_t lse_stride;
   int32_t* status; /* device int32 or NULL */
+  /* Grouped K/V heads (no counterpart in the reference, which has one K/V tensor per query head): number of
+   * heads of k, v (and v_hat); 0 means H.  Must divide H; query head h reads K/V head h / (H / Hkv).  Served
+   * by the tcgen05 forward (QFA_MODE_INT8 with v_hat, head dim 64 or 128); any other combination with
+   * Hkv != H returns QFA_ERR_SHAPE. */
+  int64_t Hkv;
 } QfaFwdArgs;
 
 QFA_API int qfa_attn_fwd(const QfaFwdArgs* args, qfa_stream_t stream);

@@ -29,7 +29,7 @@ class QfaFwdArgs(C.Structure):
                 ("q", C.c_void_p), ("q_stride", c_i64x3),
                 ("qq", QfaQuantTensor), ("k", QfaQuantTensor), ("v", QfaQuantTensor),
                 ("v_hat", C.c_void_p), ("o", C.c_void_p), ("o_stride", c_i64x3),
-                ("lse", C.c_void_p), ("lse_stride", C.c_int64), ("status", C.c_void_p)]
+                ("lse", C.c_void_p), ("lse_stride", C.c_int64), ("status", C.c_void_p), ("Hkv", C.c_int64)]
 
 
 class QfaBwdArgs(C.Structure):

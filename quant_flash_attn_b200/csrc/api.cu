@@ -97,7 +97,10 @@ QFA_API int qfa_attn_fwd(const QfaFwdArgs* a, qfa_stream_t stream) {
   if ((rc = check_quant_tensor(a->k, a->mode == QFA_MODE_INT8))) return rc;
   if ((rc = check_quant_tensor(a->v, false))) return rc;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const bool grouped = a->Hkv != 0 && a->Hkv != a->H;
+  if (grouped && (a->Hkv < 0 || a->H % a->Hkv != 0)) return QFA_ERR_SHAPE;
   if (attn_fwd_tc_supported(*a)) return attn_fwd_tc_entry(*a, s);
+  if (grouped) return QFA_ERR_SHAPE;                 // only the tcgen05 forward reads grouped K/V heads
   if (attn_fwd_shortq_supported(*a)) return attn_fwd_shortq_entry(*a, s);
   return attn_fwd_mma_entry(*a, s);
 }
@@ -161,7 +164,7 @@ QFA_API const char* qfa_strerror(int code) {
 }
 
 QFA_API const char* qfa_last_cuda_error(void) { return g_cuda_err; }
-QFA_API int qfa_version(void) { return 2; }
+QFA_API int qfa_version(void) { return 3; }
 QFA_API int64_t qfa_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 }  // extern "C"

@@ -38,7 +38,7 @@ struct TcFwdParams {
   int64_t o_stride[3];
   float* lse;
   int64_t lse_stride;
-  int H, Sq, Skv;
+  int H, Hkv, Sq, Skv;      // Hkv K/V heads serve H query heads (H / Hkv query heads each)
   float sm_scale;
   int causal;
   unsigned int epoch;   // distinguishes launches for the device-wide abort word
@@ -218,7 +218,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       for (int t = 0; t < C::NQT; ++t)
         if (n_t[t] > 0) tma_load_4d(sbase + C::Q_OFF + t * C::Q_BYTES, &tmQ, BAR(B_QFULL), 0, m0 + t * C::BM, h, b);
     }
-    const int64_t tok_k0 = static_cast<int64_t>(bh) * p.Skv;
+    const int hkv = h / (p.H / p.Hkv);            // the K/V head this query head reads
+    const int64_t tok_k0 = (static_cast<int64_t>(b) * p.Hkv + hkv) * p.Skv;
     bool ok = true;
     for (int j = 0; j < n_max && ok; ++j) {
       const int n0 = j * C::BN;
@@ -229,7 +230,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (!ok) break;
       if (lane == 0) {
         mbar_arrive_expect_tx(BAR(B_KFULL + ks), C::K_BYTES);
-        tma_load_4d(sbase + C::K_OFF + ks * C::K_BYTES, &tmK, BAR(B_KFULL + ks), 0, n0, h, b);
+        tma_load_4d(sbase + C::K_OFF + ks * C::K_BYTES, &tmK, BAR(B_KFULL + ks), 0, n0, hkv, b);
       }
       // per-column constants z_k, -sum(k), s_k
       ok = mbar_wait(BAR(B_MEMPTY + ms), ((j / C::MSTAGES) & 1) ^ 1, abort_flag, p.epoch);
@@ -264,7 +265,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         mbar_arrive_expect_tx(BAR(B_VFULL + vs), C::V_BYTES);
         for (int pn = 0; pn < C::V_PANELS; ++pn)
           tma_load_4d(sbase + C::V_OFF + vs * C::V_BYTES + pn * C::V_PANEL_BYTES, &tmV, BAR(B_VFULL + vs), pn * 64, n0,
-                      h, b);
+                      hkv, b);
       }
     }
   } else if (warp == 1) {
@@ -602,10 +603,11 @@ static int launch_tc(const QfaFwdArgs& a, cudaStream_t stream) {
       std::is_same<T, __nv_bfloat16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   bool ok = make_tmap_4d(&tmQ, a.qq.codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, D, a.Sq, a.H, a.B, a.qq.stride[2],
                          a.qq.stride[1], a.qq.stride[0], D, C::BM, qk_swz);
-  ok = ok && make_tmap_4d(&tmK, a.k.codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, D, a.Skv, a.H, a.B, a.k.stride[2],
+  const int64_t Hkv = a.Hkv ? a.Hkv : a.H;
+  ok = ok && make_tmap_4d(&tmK, a.k.codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, D, a.Skv, Hkv, a.B, a.k.stride[2],
                           a.k.stride[1], a.k.stride[0], D, C::BN, qk_swz);
-  ok = ok && make_tmap_4d(&tmV, a.v_hat, vdt, 2, D, a.Skv, a.H, a.B, 2ull * D, 2ull * D * a.Skv,
-                          2ull * D * a.Skv * a.H, 64, C::BN, CU_TENSOR_MAP_SWIZZLE_128B);
+  ok = ok && make_tmap_4d(&tmV, a.v_hat, vdt, 2, D, a.Skv, Hkv, a.B, 2ull * D, 2ull * D * a.Skv,
+                          2ull * D * a.Skv * Hkv, 64, C::BN, CU_TENSOR_MAP_SWIZZLE_128B);
   if (!ok) return cuda_fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
   TcFwdParams p;
   p.q_scale = a.qq.scale; p.q_zp = a.qq.zp; p.q_sum = a.qq.rowsum;
@@ -613,7 +615,7 @@ static int launch_tc(const QfaFwdArgs& a, cudaStream_t stream) {
   p.o = a.o;
   for (int i = 0; i < 3; ++i) p.o_stride[i] = a.o_stride[i];
   p.lse = a.lse; p.lse_stride = a.lse_stride;
-  p.H = static_cast<int>(a.H); p.Sq = static_cast<int>(a.Sq); p.Skv = static_cast<int>(a.Skv);
+  p.H = static_cast<int>(a.H); p.Hkv = static_cast<int>(Hkv); p.Sq = static_cast<int>(a.Sq); p.Skv = static_cast<int>(a.Skv);
   p.sm_scale = a.sm_scale; p.causal = a.causal; p.status = a.status;
   static std::atomic<unsigned int> epoch_counter{0};
   p.epoch = epoch_counter.fetch_add(1, std::memory_order_relaxed) + 1;

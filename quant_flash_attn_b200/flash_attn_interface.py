@@ -11,9 +11,10 @@ style, so that a model written against that interface can switch over:
 
 Layout: the kernels take element strides for every operand, so the `(B, S, H, D)` tensors are handed to
 them as transposed VIEWS; nothing is copied on the way in, and the output is written straight into a
-`(B, S, H, D)` tensor.  Grouped-query attention (fewer K/V heads than query heads) is served by
-repeating the K/V heads, packed variable-length batches by one operator call per sequence; both keep
-autograd intact.  Under the causal mask query i sees keys j <= i (flash_attn_triton.py:50), i.e. the mask
+`(B, S, H, D)` tensor.  Grouped-query attention (fewer K/V heads than query heads): without gradients the
+K/V heads are quantized once and the forward kernel maps the query heads onto them; with gradients the K/V
+heads are repeated first, so that autograd sums each group's gradients.  Packed variable-length batches are
+one operator call per sequence.  Under the causal mask query i sees keys j <= i (flash_attn_triton.py:50), i.e. the mask
 is aligned to the top-left corner when the two lengths differ.
 """
 from __future__ import annotations
@@ -22,7 +23,7 @@ import math
 
 import torch
 
-from .quant_flash_attn import quant_attention
+from .quant_flash_attn import int8_attention_forward, quant_attention, quantize_qkv
 
 
 def _scale(softmax_scale, D: int) -> float:
@@ -54,6 +55,14 @@ def quant_flash_attn_func(q, k, v, dropout_p: float = 0.0, softmax_scale=None, c
     quantized operands, as `quant_attention`)."""
     _check(q, k, v, dropout_p)
     groups = q.shape[2] // k.shape[2]
+    needs_grad = torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad)
+    if groups > 1 and not needs_grad:
+        # inference: K and V are quantized once per K/V head and the forward kernel maps query heads onto them
+        qt, kt, vt = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+        qq, kq, vq = quantize_qkv(qt, kt, vt)
+        o, _ = int8_attention_forward(qq, kq, vq, bool(causal), _scale(softmax_scale, q.shape[3]), q.dtype,
+                                      o=torch.empty_like(qt))
+        return o.transpose(1, 2).contiguous()
     k, v = _repeat_kv_heads(k, groups), _repeat_kv_heads(v, groups)
     o = quant_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), bool(causal), _scale(softmax_scale, q.shape[3]))
     # the operator wrote its result in q's memory layout, so this view is already contiguous (B,Sq,H,D)

@@ -135,14 +135,19 @@ def quantize_qkv(q, k, v):
 def int8_attention_forward(qq, kq, vq, causal: bool, sm_scale: float, dtype: torch.dtype,
                            o: torch.Tensor | None = None, lse: torch.Tensor | None = None):
     """Forward of the int8 operator on already quantized operands (tuples from `quantize_qkv`).
-    Returns (o, lse); lse is (B,H,Sq) fp32 natural-log."""
+    Returns (o, lse); lse is (B,H,Sq) fp32 natural-log.  k and v may have fewer heads than q (a divisor of
+    H): query head h then reads K/V head h // (H / Hkv)."""
     qc, qs, qz, qsum = qq[:4]
     kc, ks, kz, ksum = kq[:4]
     vc, vs, vz = vq[:3]
     vhat = vq[4] if len(vq) > 4 else None
     B, H, Sq, D = qc.shape
-    Skv = kc.shape[2]
+    Hkv, Skv = kc.shape[1], kc.shape[2]
     _check_head_dim(D)
+    if H % Hkv != 0 or vc.shape[1] != Hkv:
+        raise ValueError("the number of query heads must be a multiple of the number of K/V heads")
+    if Hkv != H and vhat is None:
+        raise ValueError("grouped K/V heads need the dequantized V from quantize_qkv")
     if o is None:
         o = torch.empty((B, H, Sq, D), dtype=dtype, device=qc.device)
     if lse is None:
@@ -156,7 +161,7 @@ def int8_attention_forward(qq, kq, vq, causal: bool, sm_scale: float, dtype: tor
         qq=_quant_tensor(qc, qs, qz, qsum), k=_quant_tensor(kc, ks, kz, ksum), v=_quant_tensor(vc, vs, vz),
         v_hat=vhat.data_ptr() if vhat is not None else None,
         o=o.data_ptr(), o_stride=_s3(o), lse=lse.data_ptr(), lse_stride=Sq,
-        status=status.data_ptr() if status is not None else None)
+        status=status.data_ptr() if status is not None else None, Hkv=Hkv)
     with torch.cuda.device(qc.device):
         rc = _lib.load().qfa_attn_fwd(C.byref(args), _stream(qc))
     _lib.check(rc, "qfa_attn_fwd")

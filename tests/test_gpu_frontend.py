@@ -68,9 +68,31 @@ def test_grouped_kv_heads(qfa):
     want_dv = vr.grad.float().view(B, S, Hkv, H // Hkv, D).sum(3)
     _close(k.grad, want_dk, what="dk")
     _close(v.grad, want_dv, what="dv")
-    # packed K/V form
+    # packed K/V form; without gradients the forward kernel reads the two K/V heads directly (no repetition):
+    # same operands, same arithmetic, same bits
     o3 = qfa.quant_flash_attn_kvpacked_func(q.detach(), torch.stack([k.detach(), v.detach()], dim=2), causal=True)
     assert torch.equal(o3, o)
+    with torch.no_grad():
+        o4 = qfa.quant_flash_attn_func(q, k, v, causal=True)
+    assert torch.equal(o4, o)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_grouped_kv_heads_native_forward(qfa, dtype):
+    """(B,H,S,D) operator with 8 query heads on 2 K/V heads at D=128, ragged lengths, against the oracle fed with
+    the repeated heads."""
+    B, H, Hkv, Sq, Skv, D = 2, 8, 2, 150, 300, 128
+    q = _gen((B, H, Sq, D), dtype, 91)
+    k = _gen((B, Hkv, Skv, D), dtype, 92)
+    v = _gen((B, Hkv, Skv, D), dtype, 93)
+    sm = 1.0 / math.sqrt(D)
+    qq, kq, vq = qfa.quantize_qkv(q.cuda(), k.cuda(), v.cuda())
+    o, lse = qfa.int8_attention_forward(qq, kq, vq, False, sm, dtype)
+    rep = lambda t: tuple(x.repeat_interleave(H // Hkv, dim=1) for x in _cpu_quant(t))
+    o_ref, lse_ref, _ = oracle.int8_mode_forward(q, k.repeat_interleave(H // Hkv, dim=1), v.repeat_interleave(H // Hkv, dim=1),
+                                                 False, sm, quant=(_cpu_quant(qq), rep(kq), rep(vq)), round_output=False)
+    assert (lse.cpu() - lse_ref).abs().max() <= 2e-3
+    _close(o, o_ref, what="o")
 
 
 def test_varlen_batch(qfa):

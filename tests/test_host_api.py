@@ -26,7 +26,7 @@ def test_library_exports_every_declared_symbol(lib):
     raw = C.CDLL(_lib.LIB_PATH)
     for name in declared:
         assert hasattr(raw, name), name
-    assert lib.qfa_version() == 2
+    assert lib.qfa_version() == 3
 
 
 def test_struct_layout_matches_header():
@@ -34,7 +34,8 @@ def test_struct_layout_matches_header():
     assert C.sizeof(_lib.QfaQuantTensor) == 56
     assert _lib.QfaFwdArgs.B.offset == 16 and _lib.QfaFwdArgs.q.offset == 56
     assert _lib.QfaFwdArgs.qq.offset == 88 and _lib.QfaFwdArgs.v_hat.offset == 88 + 3 * 56
-    assert C.sizeof(_lib.QfaFwdArgs) == 88 + 3 * 56 + 8 + 8 + 24 + 8 + 8 + 8
+    assert C.sizeof(_lib.QfaFwdArgs) == 88 + 3 * 56 + 8 + 8 + 24 + 8 + 8 + 8 + 8
+    assert _lib.QfaFwdArgs.Hkv.offset == C.sizeof(_lib.QfaFwdArgs) - 8
     assert _lib.QfaBwdArgs.B.offset == 24 and _lib.QfaBwdArgs.qq.offset == 96
 
 
