@@ -22,7 +22,9 @@ import os
 import sys
 
 os.environ["TRITON_INTERPRET"] = "1"
-REF = os.environ.get("QFA_REFERENCE_DIR", "/root/reference")
+if "QFA_REFERENCE_DIR" not in os.environ:
+    sys.exit("set QFA_REFERENCE_DIR to a checkout of the reference project (yisunlp/quant_flash_attn)")
+REF = os.environ["QFA_REFERENCE_DIR"]
 sys.path.insert(0, REF)
 
 import numpy as np  # noqa: E402

@@ -17,7 +17,9 @@ import sys
 import numpy as np
 import torch
 
-REF = os.environ.get("QFA_REFERENCE_DIR", "/root/reference")
+if "QFA_REFERENCE_DIR" not in os.environ:
+    sys.exit("set QFA_REFERENCE_DIR to a checkout of the reference project (yisunlp/quant_flash_attn)")
+REF = os.environ["QFA_REFERENCE_DIR"]
 OUT = sys.argv[1] if len(sys.argv) > 1 else os.path.dirname(os.path.abspath(__file__))
 
 
