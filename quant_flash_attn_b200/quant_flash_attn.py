@@ -185,8 +185,10 @@ def dequantize_16bit(codes, scale, zp, dtype: torch.dtype) -> torch.Tensor:
     return out
 
 
-def int8_attention_backward(qq, kq, vq, causal, sm_scale, o, lse, do):
-    """Backward of the int8 operator; returns (dq, dk, dv) in o's dtype."""
+def int8_attention_backward(qq, kq, vq, causal, sm_scale, o, lse, do, use_tc: bool | None = None):
+    """Backward of the int8 operator; returns (dq, dk, dv) in o's dtype.  `use_tc=False` withholds the
+    dequantized operands, which sends the call to the general (mma.sync) kernels: two independent
+    implementations of the same arithmetic, used to cross-check each other at sizes the oracle cannot reach."""
     qc, qs, qz, qsum = qq[:4]
     kc, ks, kz, ksum = kq[:4]
     vc, vs, vz = vq[:3]
@@ -200,7 +202,7 @@ def int8_attention_backward(qq, kq, vq, causal, sm_scale, o, lse, do):
     delta = torch.empty((B, H, Sq), dtype=torch.float32, device=dev)
     # the tcgen05 kernels take the dequantized operands as 16-bit tensors and need no dQ scratch; the
     # general kernel (non-positive sm_scale) accumulates dQ in fp32 scratch instead
-    use_tc = float(sm_scale) > 0.0
+    use_tc = float(sm_scale) > 0.0 and (use_tc is None or bool(use_tc))
     q_hat = k_hat = v_hat = dq_accum = None
     if use_tc:
         q_hat = dequantize_16bit(qc, qs, qz, dtype)

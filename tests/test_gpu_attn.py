@@ -222,6 +222,47 @@ def test_host_pipeline_matches_device_operator(qfa, causal):
     assert torch.equal(got2, want)
 
 
+def test_headline_size_cross_checks(qfa):
+    """The benchmark's full size (B4 H32 S4096 D128, outlier channels).  The oracle is too slow for 128 heads, so:
+    two whole heads against the oracle, and every head of the tcgen05 forward against the mma.sync forward (an
+    independent implementation of the same arithmetic, reached by withholding the dequantized V)."""
+    B, H, S, D = 4, 32, 4096, 128
+    g = torch.Generator(device="cuda").manual_seed(7)
+    q, k, v = (torch.randn(B, H, S, D, device="cuda", dtype=torch.bfloat16, generator=g) for _ in range(3))
+    idx = torch.tensor([5, 77], device="cuda")
+    for t in (q, k, v):
+        t[..., idx] *= 20.0
+    sm = 1.0 / math.sqrt(D)
+    qq, kq, vq = qfa.quantize_qkv(q, k, v)
+    o_tc, lse_tc = qfa.int8_attention_forward(qq, kq, vq, False, sm, torch.bfloat16)
+    o_mma, lse_mma = qfa.int8_attention_forward(qq, kq, vq[:4], False, sm, torch.bfloat16)
+    assert torch.isfinite(o_tc).all() and torch.isfinite(lse_tc).all()
+    assert (lse_tc - lse_mma).abs().max().item() <= 2e-3
+    _close(o_tc, o_mma.float(), rel=REL_TOL + HALF_ULP[torch.bfloat16], what="tc vs mma")
+    for b, h in ((0, 0), (3, 17)):
+        sl = (slice(b, b + 1), slice(h, h + 1))
+        quant = tuple(tuple(x[sl].cpu() for x in _cpu_quant_dev(t)) for t in (qq, kq, vq))
+        o_ref, lse_ref, _ = oracle.int8_mode_forward(q[sl].cpu(), k[sl].cpu(), v[sl].cpu(), False, sm, quant=quant,
+                                                     round_output=False)
+        assert (lse_tc[sl].cpu() - lse_ref).abs().max().item() <= 2e-3
+        # outlier channels make the softmax of many rows sit on a few keys, so the 16-bit rounding of P before P.V
+        # (the reference's semantics, quant_flash_attn.py:75; the oracle keeps P in fp32) does not average out:
+        # allow half an ulp of the dtype on top of the usual bound, as in test_int8_mode_growing_logits
+        _close(o_tc[sl], o_ref, rel=REL_TOL + HALF_ULP[torch.bfloat16], what=f"head ({b},{h})")
+    # backward: tcgen05 kernels against the mma.sync kernels on all 128 heads
+    do = torch.randn(B, H, S, D, device="cuda", dtype=torch.bfloat16, generator=g)
+    grads_tc = qfa.int8_attention_backward(qq, kq, vq, False, sm, o_tc, lse_tc, do)
+    grads_mma = qfa.int8_attention_backward(qq, kq, vq, False, sm, o_tc, lse_tc, do, use_tc=False)
+    for name, a, b_ in zip(("dq", "dk", "dv"), grads_tc, grads_mma):
+        _close(a, b_.float(), rel=REL_TOL_GRAD[torch.bfloat16], what=name + " tc vs mma")
+
+
+def _cpu_quant_dev(t):
+    """Like _cpu_quant but keeps the tensors on the device and 4-D / 3-D sliceable: (codes, scale, zp, rowsum)."""
+    codes, scale, zp, rowsum = t[:4]
+    return (codes, scale.float().squeeze(-1), zp.squeeze(-1), rowsum)
+
+
 def test_training_shape_properties(qfa):
     """BASELINE config 3 (B8 H16 S2048 D64 causal) at full size: the oracle is too slow there, so
     check size-independent properties: finite outputs, row 0 attends only to token 0, gradient
