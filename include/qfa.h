@@ -181,20 +181,34 @@ QFA_API int qfa_attn_bwd(const QfaBwdArgs* args, qfa_stream_t stream);
  * memory at call time, e.g. an inference-engine plugin whose enqueue hook must not allocate, or a
  * process that gave the whole device to a memory pool at start-up.
  *
- * Identical to qfa_attn_bwd except that `dq_accum` in `args` is ignored: the fp32 dQ accumulator
- * is a fixed array inside the library (qfa_static_scratch_capacity() floats = 16 MiB, resident
- * on every GPU that loads the library until the process exits).  The call allocates and frees
- * nothing, neither through CUDA nor through any library.
+ * Same validation, arithmetic and outputs as qfa_attn_bwd, with two differences.  (1) `dq_accum` in `args` is
+ * ignored: the fp32 dQ accumulator is a fixed array inside the library (qfa_static_scratch_capacity() floats
+ * = 16 MiB, resident on every GPU that loads the library until the process exits).  (2) `q_hat`, `k_hat` and
+ * `v_hat` are ignored too, so the call always runs the general (mma.sync) backward kernels, the ones that
+ * accumulate dQ in scratch memory; these are slower than the tcgen05 kernels qfa_attn_bwd picks when the
+ * dequantized operands are supplied.  The call itself requests no memory: it makes no cudaMalloc / cudaFree
+ * and calls no allocating library routine.
  *   - B*H*Sq*D must not exceed qfa_static_scratch_capacity(); larger problems return
  *     QFA_ERR_TOO_LARGE before anything is launched.
- *   - The first call on each device looks up the array's device address (the device must be
- *     current, as for every entry point); make that first call outside any stream capture.
- *   - All calls share the one array; the used part is zero-filled at the start of each call and
- *     holds stale data otherwise.  Two calls whose kernels overlap on the GPU (different
- *     streams) race on it: serialize them. */
+ *   - The FIRST call on each device does one-time set-up with that device current: it looks up the array's
+ *     device address, which makes the CUDA runtime load the module that holds the 16 MiB array, and the first
+ *     launch loads the kernels.  That set-up does take device memory from the driver.  A host that is about
+ *     to hand the whole device to its own pool must therefore make one (small) call first, at start-up, and
+ *     outside any stream capture; later calls find everything in place.
+ *   - All calls share the one array; the used part is zero-filled on the caller's stream at the start of
+ *     each call and holds the previous call's data otherwise.  Two calls whose kernels overlap on the GPU
+ *     (different streams) race on it: serialize them. */
 QFA_API int qfa_attn_bwd_static_scratch(const QfaBwdArgs* args, qfa_stream_t stream);
 /* Capacity, in floats, of the accumulator used by qfa_attn_bwd_static_scratch. */
 QFA_API int64_t qfa_static_scratch_capacity(void);
+
+/* Self-test of the bounded waits.  No counterpart in the reference (its kernels have no device-side waits).
+ * Launches one tiny kernel whose only thread waits, for at most `budget_ns` nanoseconds (1 .. 100 000 000), on a
+ * barrier that nothing completes.  The wait gives up, the kernel stores QFA_STATUS_WAIT_TIMEOUT into `status`
+ * (device-accessible int32, required) and returns normally: nothing traps, the context stays usable and later
+ * launches of every entry point are unaffected.  Lets a deployment check the time-out reporting path end to
+ * end without provoking a fault. */
+QFA_API int qfa_selftest_wait_timeout(uint64_t budget_ns, int32_t* status, qfa_stream_t stream);
 
 /* Text for a return / status code. */
 QFA_API const char* qfa_strerror(int code);

@@ -59,6 +59,7 @@ SIGNATURES = {
     "qfa_attn_bwd": (C.c_int, [C.POINTER(QfaBwdArgs), C.c_void_p]),
     "qfa_attn_bwd_static_scratch": (C.c_int, [C.POINTER(QfaBwdArgs), C.c_void_p]),
     "qfa_static_scratch_capacity": (C.c_int64, []),
+    "qfa_selftest_wait_timeout": (C.c_int, [C.c_uint64, C.c_void_p, C.c_void_p]),
     "qfa_strerror": (C.c_char_p, [C.c_int]),
     "qfa_last_cuda_error": (C.c_char_p, []),
     "qfa_version": (C.c_int, []),
@@ -100,3 +101,42 @@ def check(rc: int, what: str):
 
 def launch_count() -> int:
     return int(load().qfa_launch_count())
+
+
+# ----------------------------------------------------------------------------------------------- kernel status
+# Every attention launch gets a status word.  It lives in pinned HOST memory, which the GPU writes directly
+# (pinned memory is mapped into the device's address space), so it can be read back without a device
+# synchronisation: each operator looks at it before its next launch on that device, and
+# `raise_if_kernel_status(device, synchronize=True)` checks it on demand.
+_status_words = {}
+
+
+def status_word(device):
+    """The (1,) int32 pinned host tensor that kernels launched on `device` report into."""
+    import torch
+    idx = torch.device(device).index
+    if idx is None:
+        idx = torch.cuda.current_device()
+    t = _status_words.get(idx)
+    if t is None:
+        with _lock:
+            t = _status_words.get(idx)
+            if t is None:
+                t = torch.zeros(1, dtype=torch.int32).pin_memory()
+                _status_words[idx] = t
+    return t
+
+
+def raise_if_kernel_status(device, synchronize: bool = False):
+    """Raises if a kernel launched earlier on `device` reported a status (a bounded wait that ran out); the word
+    is cleared, so the error is reported once.  With `synchronize` the device is synchronised first, so every
+    launch made so far is covered."""
+    import torch
+    if synchronize:
+        torch.cuda.synchronize(device)
+    t = status_word(device)
+    code = int(t[0])
+    if code:
+        t.zero_()
+        raise RuntimeError(f"a qfa kernel on {torch.device(device)} reported status {code}: "
+                           f"{load().qfa_strerror(code).decode()}; its outputs are not valid")

@@ -12,6 +12,13 @@ static thread_local char g_cuda_err[256] = "";
 
 void note_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
+unsigned int next_launch_epoch() {
+  static std::atomic<unsigned int> counter{0};
+  unsigned int e = counter.fetch_add(1, std::memory_order_relaxed) + 1;
+  if (e == 0) e = counter.fetch_add(1, std::memory_order_relaxed) + 1;   // 0 means "no launch ever timed out"
+  return e;
+}
+
 int cuda_fail(cudaError_t e, const char* what) {
   snprintf(g_cuda_err, sizeof(g_cuda_err), "%s: %s", what, cudaGetErrorString(e));
   return QFA_ERR_CUDA;
@@ -28,6 +35,7 @@ int attn_fwd_mma_entry(const QfaFwdArgs& a, cudaStream_t stream);
 int attn_fwd_tc_supported(const QfaFwdArgs& a);
 int attn_fwd_tc_entry(const QfaFwdArgs& a, cudaStream_t stream);
 int attn_bwd_mma_entry(const QfaBwdArgs& a, float* dq_accum, cudaStream_t stream);
+int wait_timeout_selftest_entry(uint64_t budget_ns, int32_t* status, cudaStream_t stream);
 int attn_fwd_shortq_supported(const QfaFwdArgs& a);
 int attn_fwd_shortq_entry(const QfaFwdArgs& a, cudaStream_t stream);
 int attn_bwd_shortq_supported(const QfaBwdArgs& a);
@@ -146,6 +154,10 @@ QFA_API int qfa_attn_bwd(const QfaBwdArgs* a, qfa_stream_t stream) {
   return attn_bwd_mma_entry(*a, a->dq_accum, reinterpret_cast<cudaStream_t>(stream));
 }
 
+QFA_API int qfa_selftest_wait_timeout(uint64_t budget_ns, int32_t* status, qfa_stream_t stream) {
+  return wait_timeout_selftest_entry(budget_ns, status, reinterpret_cast<cudaStream_t>(stream));
+}
+
 QFA_API const char* qfa_strerror(int code) {
   switch (code) {
     case QFA_OK: return "ok";
@@ -164,7 +176,7 @@ QFA_API const char* qfa_strerror(int code) {
 }
 
 QFA_API const char* qfa_last_cuda_error(void) { return g_cuda_err; }
-QFA_API int qfa_version(void) { return 3; }
+QFA_API int qfa_version(void) { return 4; }
 QFA_API int64_t qfa_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 }  // extern "C"

@@ -52,23 +52,6 @@ struct TcBwdParams {
   int32_t* status;
 };
 
-// Optional timeline tracing for development builds (-DQFA_TC_TRACE): CTA 0 writes clock64() stamps of its
-// first 16 steps into the buffer passed as `status` (interpreted as long long[2][16][16]).
-#ifdef QFA_TC_TRACE
-#ifndef QFA_TRACE_KV
-#define QFA_TRACE_KV 1
-#endif
-#define QFA_BTRACE(role, it, idx)                                                                   \
-  do {                                                                                              \
-    if (KV_PASS == bool(QFA_TRACE_KV) && blockIdx.x == 0 && (it) < 16 && p.status)                  \
-      reinterpret_cast<long long*>(p.status)[((role) * 16 + (it)) * 16 + (idx)] = clock64();        \
-  } while (0)
-#else
-#define QFA_BTRACE(role, it, idx) \
-  do {                            \
-  } while (0)
-#endif
-
 template <int D>
 struct BwdTcCfg {
   static constexpr int BM = 128, BN = 128, STAGES = 2;
@@ -294,11 +277,9 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
       for (int it = 0; it < n_steps && ok; ++it) {
         const int st = it % C::STAGES;
         const uint32_t stage = sbase + C::ST_OFF + st * C::ST_BYTES;
-        QFA_BTRACE(1, it, 0);
         ok = mbar_wait(BAR(B_YFULL + st), (it / C::STAGES) & 1, abort_flag, p.epoch);
         if (!ok) break;
         tc_fence_after_sync();
-        QFA_BTRACE(1, it, 1);
         // T1 = Xc Yc^T (int8), T2 = Xh Ya^T (16 bit, K-major x K-major).  They overwrite the P / dS of the previous
         // step: the tensor pipe runs MMAs in issue order, so they start after that step's accumulating MMAs
         {
@@ -317,7 +298,6 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
           }
           mma_commit(BAR(B_T2));
         }
-        QFA_BTRACE(1, it, 2);
         // accumulate with P / dS read from tensor memory, one 16-column k-step at a time as the softmax warps hand
         // the blocks over (the two column halves advance side by side)
         const uint64_t db1 = make_smem_desc(stage + C::C_BYTES, C::PANEL_BYTES, 1024, kSwizzle128B);               // dO (pass KV)
@@ -329,7 +309,6 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
           ok = mbar_wait(BAR(B_PD + hf), it & 1, abort_flag, p.epoch);
           if (!ok) break;
           tc_fence_after_sync();
-          QFA_BTRACE(1, it, 3 + i);
           if (KV_PASS) {    // acc1 (dV) += P^T dO : right operand = the Ya tile (dO) viewed MN-major
 #pragma unroll
             for (int kk = kk0; kk < kk0 + 2; ++kk)
@@ -343,7 +322,6 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
                        (it > 0 || i > 0 || kk > kk0) ? 1u : 0u);
         }
         if (!ok) break;
-        QFA_BTRACE(1, it, 11);
         mma_commit(BAR(B_YEMPTY + st));
         if (it == n_steps - 1) mma_commit(BAR(B_ACC));
       }
@@ -388,16 +366,12 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
     for (int it = 0; it < n_steps && ok; ++it) {
       const int st = it % C::STAGES;
       const int c0 = (j_begin + it) * C::BN;
-      const bool tr = (sw == 0 && lane == 0);
-      if (tr) QFA_BTRACE(0, it, 0);
       ok = mbar_wait(BAR(B_MFULL + st), (it / C::STAGES) & 1, abort_flag, p.epoch);
       if (ok) ok = mbar_wait(BAR(B_T1), it & 1, abort_flag, p.epoch);
-      if (tr) QFA_BTRACE(0, it, 1);
       if (ok) ok = mbar_wait(BAR(B_T2), it & 1, abort_flag, p.epoch);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
-      if (tr) QFA_BTRACE(0, it, 2);
       const float4* meta = reinterpret_cast<const float4*>(smem + C::M_OFF + st * C::M_BYTES) + (16 * ch + q) * 5;
       // visible column range of each row, relative to (tile start + 64*ch + 2q)
       int lo[2], hi[2];
@@ -420,7 +394,6 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
 #pragma unroll
       for (int blk = 0; blk < 4; ++blk) {
         tmem_wait_ld_use(sreg[blk & 1], dreg[blk & 1]);
-        if (tr) QFA_BTRACE(0, it, 3 + 2 * blk);
         if (blk + 1 < 4) {
           tmem_ld_16x256b_x2(tT1 + (blk + 1) * 16, sreg[(blk + 1) & 1]);
           tmem_ld_16x256b_x2(tT2 + (blk + 1) * 16, dreg[(blk + 1) & 1]);
@@ -441,7 +414,6 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(BAR(B_PD + 2 * ch + (blk >> 1)));
-          if (tr) QFA_BTRACE(0, it, 4 + 2 * blk);
         }
       }
     }
@@ -489,12 +461,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
     tc_fence_after_sync();
     tmem_dealloc(tmem, C::TMEM_COLS);
   }
-#ifndef QFA_TC_TRACE
   if (tid == 0 && *abort_flag && p.status) *p.status = QFA_STATUS_WAIT_TIMEOUT;
-#endif
 }
-
-static std::atomic<unsigned int> g_bwd_epoch{0x40000000u};
 
 template <typename T, int D, bool KV_PASS>
 static int launch_bwd_tc(const QfaBwdArgs& a, cudaStream_t stream) {
@@ -539,19 +507,18 @@ static int launch_bwd_tc(const QfaBwdArgs& a, cudaStream_t stream) {
   p.rows_total = static_cast<int>(Sx);
   p.cols_total = static_cast<int>(Sy);
   p.sm_scale = a.sm_scale; p.causal = a.causal; p.status = a.status;
-  p.epoch = g_bwd_epoch.fetch_add(1, std::memory_order_relaxed) + 1;
+  p.epoch = next_launch_epoch();
   auto kern = attn_bwd_tc_kernel<T, D, KV_PASS>;
-  static bool attr_done[64] = {};
-  int devid = 0;
-  QFA_CUDA_TRY(cudaGetDevice(&devid));
-  if (devid < 64 && !attr_done[devid]) {
+  static DeviceOnce attr_done;
+  int rc = once_per_device(attr_done, [&]() -> int {
     QFA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
     // the register hand-over inside the kernel assumes this many registers per thread at launch
     cudaFuncAttributes fa;
     QFA_CUDA_TRY(cudaFuncGetAttributes(&fa, kern));
     if (fa.numRegs < C::LAUNCH_REGS) return cuda_fail(cudaErrorLaunchOutOfResources, "backward kernel register pool");
-    attr_done[devid] = true;
-  }
+    return QFA_OK;
+  });
+  if (rc != QFA_OK) return rc;
   const int64_t n_ctas = ((Sx + C::BM - 1) / C::BM) * a.B * a.H;
   if (n_ctas > 0x7fffffffLL) return QFA_ERR_SHAPE;
   kern<<<static_cast<unsigned>(n_ctas), C::THREADS, C::SMEM, stream>>>(tmXc, tmXh, tmYc, tmYa, tmYb, p);

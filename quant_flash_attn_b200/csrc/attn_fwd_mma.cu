@@ -340,13 +340,12 @@ template <typename T, int D, bool INT8>
 static int launch_fwd(const FwdDev& dev, int B, cudaStream_t stream) {
   using C = FwdCfg<D, INT8>;
   auto kern = attn_fwd_mma_kernel<T, D, INT8>;
-  static bool attr_done[64] = {};
-  int devid = 0;
-  QFA_CUDA_TRY(cudaGetDevice(&devid));
-  if (devid < 64 && !attr_done[devid]) {
+  static DeviceOnce attr_done;
+  int rc = once_per_device(attr_done, [&]() -> int {
     QFA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
-    attr_done[devid] = true;
-  }
+    return QFA_OK;
+  });
+  if (rc != QFA_OK) return rc;
   const int64_t n_ctas = static_cast<int64_t>((dev.Sq + C::BM - 1) / C::BM) * B * dev.H;
   if (n_ctas > 0x7fffffffLL) return QFA_ERR_SHAPE;
   kern<<<static_cast<unsigned>(n_ctas), C::THREADS, C::SMEM, stream>>>(dev);

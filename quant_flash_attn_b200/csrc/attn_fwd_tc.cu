@@ -45,20 +45,6 @@ struct TcFwdParams {
   int32_t* status;
 };
 
-// Optional timeline tracing for development builds (-DQFA_TC_TRACE): CTA 0 writes clock64() stamps of its
-// first 16 K/V steps into the buffer passed as `status` (interpreted as long long[2][16][2][8]).
-#ifdef QFA_TC_TRACE
-#define QFA_TRACE(role, j, t, idx)                                                                          \
-  do {                                                                                                      \
-    if (blockIdx.x == 0 && (j) < 16 && p.status)                                                            \
-      reinterpret_cast<long long*>(p.status)[(((role) * 16 + (j)) * 2 + (t)) * 8 + (idx)] = clock64();      \
-  } while (0)
-#else
-#define QFA_TRACE(role, j, t, idx) \
-  do {                             \
-  } while (0)
-#endif
-
 template <int D>
 struct TcCfg {
   static constexpr int BM = 128, BN = 128, NQT = 2;
@@ -314,13 +300,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         bool kwaited = false;
         for (int t = 0; t < C::NQT && ok; ++t) {
           if (j < n_t[t]) {
-            QFA_TRACE(1, j, t, 0);
             ok = mbar_wait(BAR(B_PFULL + t), j & 1, abort_flag, p.epoch);
             if (!ok) break;
             tc_fence_after_sync();
-            QFA_TRACE(1, j, t, 1);
             issue_pv(j, t);
-            QFA_TRACE(1, j, t, 2);
           }
           if (j + 1 < n_t[t]) {
             if (!kwaited) {
@@ -330,7 +313,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
               kwaited = true;
             }
             issue_qk(j + 1, t);
-            QFA_TRACE(1, j, t, 3);
           }
         }
         if (!ok) break;
@@ -393,14 +375,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     for (int j = 0; j < n_max && ok; ++j) {
       const int ms = j % C::MSTAGES;
       if (j < my_n) {
-        const bool tr = (sw == 8 * t && lane == 0);
-        if (tr) QFA_TRACE(0, j, t, 0);
         ok = mbar_wait(BAR(B_MFULL + ms), (j / C::MSTAGES) & 1, abort_flag, p.epoch);
         if (ok) ok = mbar_wait(BAR(B_SFULL + t), j & 1, abort_flag, p.epoch);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after_sync();
-        if (tr) QFA_TRACE(0, j, t, 1);
         const float4* meta = reinterpret_cast<const float4*>(smem + C::M_OFF + ms * C::M_BYTES) + 3 * q;
         const int n0 = j * C::BN;
         int lim[2];                                   // first masked column of each row, relative to 2q
@@ -458,7 +437,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           }
         }
         if (masked) run_tile(std::false_type{}, std::true_type{}); else run_tile(std::false_type{}, std::false_type{});
-        if (tr) QFA_TRACE(0, j, t, 3);
         quad_max();
 
         // ---- rare: some row exceeded its reference by more than 2^kGrow
@@ -528,14 +506,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (lane == 0) mbar_arrive(BAR(B_MEMPTY + ms));
 #pragma unroll
         for (int k = 0; k < 2; ++k) l_run[k] += lsum2[k].x + lsum2[k].y;
-        if (tr) QFA_TRACE(0, j, t, 5);
         tmem_st_16x128b_x16(tS, pw);
-        if (tr) QFA_TRACE(0, j, t, 6);
         tmem_wait_st();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(BAR(B_PFULL + t));
-        if (tr) QFA_TRACE(0, j, t, 7);
       } else {
         // this query tile is done (causal): keep the per-column ring moving for the other tile
         ok = mbar_wait(BAR(B_MFULL + ms), (j / C::MSTAGES) & 1, abort_flag, p.epoch);
@@ -589,9 +564,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     tc_fence_after_sync();
     tmem_dealloc(tmem, C::TMEM_COLS);
   }
-#ifndef QFA_TC_TRACE
   if (tid == 0 && *abort_flag && p.status) *p.status = QFA_STATUS_WAIT_TIMEOUT;
-#endif
 }
 
 template <typename T, int D>
@@ -617,24 +590,49 @@ static int launch_tc(const QfaFwdArgs& a, cudaStream_t stream) {
   p.lse = a.lse; p.lse_stride = a.lse_stride;
   p.H = static_cast<int>(a.H); p.Hkv = static_cast<int>(Hkv); p.Sq = static_cast<int>(a.Sq); p.Skv = static_cast<int>(a.Skv);
   p.sm_scale = a.sm_scale; p.causal = a.causal; p.status = a.status;
-  static std::atomic<unsigned int> epoch_counter{0};
-  p.epoch = epoch_counter.fetch_add(1, std::memory_order_relaxed) + 1;
-  if (p.epoch == 0) p.epoch = epoch_counter.fetch_add(1, std::memory_order_relaxed) + 1;
+  p.epoch = next_launch_epoch();
   auto kern = attn_fwd_tc_kernel<T, D>;
-  static bool attr_done[64] = {};
-  int devid = 0;
-  QFA_CUDA_TRY(cudaGetDevice(&devid));
-  if (devid < 64 && !attr_done[devid]) {
+  static DeviceOnce attr_done;
+  int rc = once_per_device(attr_done, [&]() -> int {
     QFA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
     // the register hand-over inside the kernel assumes this many registers per thread at launch
     cudaFuncAttributes fa;
     QFA_CUDA_TRY(cudaFuncGetAttributes(&fa, kern));
     if (fa.numRegs < C::LAUNCH_REGS) return cuda_fail(cudaErrorLaunchOutOfResources, "forward kernel register pool");
-    attr_done[devid] = true;
-  }
+    return QFA_OK;
+  });
+  if (rc != QFA_OK) return rc;
   const int64_t n_ctas = ((a.Sq + C::NQT * C::BM - 1) / (C::NQT * C::BM)) * a.B * a.H;
   if (n_ctas > 0x7fffffffLL) return QFA_ERR_SHAPE;
   kern<<<static_cast<unsigned>(n_ctas), C::THREADS, C::SMEM, stream>>>(tmQ, tmK, tmV, p);
+  note_launch();
+  QFA_CUDA_TRY(cudaGetLastError());
+  return QFA_OK;
+}
+
+// ------------------------------------------------------------------ self-test of the bounded wait
+// One thread waits on an mbarrier that nothing ever arrives at, with a short budget; the wait must give up, raise
+// the abort flag and the device-wide abort word (shared with the forward kernels of this file) and report
+// QFA_STATUS_WAIT_TIMEOUT through `status`.  The kernel returns normally and the context stays usable.
+__global__ void wait_timeout_selftest_kernel(unsigned long long budget_ns, unsigned int epoch, int32_t* status) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int abort_word;
+  volatile int* abort_flag = &abort_word;
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) mbar_wait(smem_u32(&bar), 0, abort_flag, epoch, budget_ns);
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag && status) *status = QFA_STATUS_WAIT_TIMEOUT;
+}
+
+int wait_timeout_selftest_entry(uint64_t budget_ns, int32_t* status, cudaStream_t stream) {
+  if (!status) return QFA_ERR_NULL;
+  if (budget_ns == 0 || budget_ns > 100ull * 1000 * 1000) return QFA_ERR_SHAPE;      // at most 100 ms
+  wait_timeout_selftest_kernel<<<1, 32, 0, stream>>>(budget_ns, next_launch_epoch(), status);
   note_launch();
   QFA_CUDA_TRY(cudaGetLastError());
   return QFA_OK;

@@ -39,6 +39,7 @@ struct ShortQDev {
   int64_t lse_stride;
   int H, Sq, Skv;
   float sm_scale;
+  unsigned int epoch;    // launch epoch for the bounded waits (next_launch_epoch)
   int32_t* status;
 };
 
@@ -119,6 +120,7 @@ struct KvRing {
   const uint16_t* scale;
   const int8_t* zp;
   int skv, n_tiles;
+  unsigned int epoch;
   float2 pend;
   int pend_slot;
 
@@ -142,9 +144,10 @@ struct KvRing {
     bar0 = smem_u32(bars);
     abort_flag = reinterpret_cast<volatile int*>(bars + NST * 8);
     src = kvc; scale = p.kv.scale + tok0; zp = p.kv.zp + tok0; skv = p.Skv; n_tiles = tiles;
+    epoch = p.epoch;
     pend_slot = -1;
     if (tid == 0) {
-      *abort_flag = 0;
+      *abort_flag = sm100::launch_aborted(p.epoch) ? 1 : 0;   // a CTA of this launch already gave up: drain quickly
       for (int s = 0; s < NST; ++s) sm100::mbar_init(bar0 + 8 * s, 1);
       sm100::fence_barrier_init();
     }
@@ -158,7 +161,7 @@ struct KvRing {
   template <typename T>
   __device__ __forceinline__ bool commit(uint8_t* sKV, int tile, int tid) const {
     const int s = tile % NST;
-    if (!sm100::mbar_wait(bar0 + 8 * s, (tile / NST) & 1, abort_flag, 0xffffffffu)) return false;
+    if (!sm100::mbar_wait(bar0 + 8 * s, (tile / NST) & 1, abort_flag, epoch)) return false;
     const uint8_t* cs = codes + s * C::CODE_BYTES;
     const float2* ms = meta + s * C::BN;
 #pragma unroll
@@ -580,20 +583,17 @@ __global__ void __launch_bounds__(128, MT == 1 ? 4 : 1) attn_bwd_shortq_kernel(S
 
 // ------------------------------------------------------------------------------------------------ host
 template <typename K>
-static int set_smem(K kern, int bytes, bool* done) {
-  int devid = 0;
-  QFA_CUDA_TRY(cudaGetDevice(&devid));
-  if (devid < 64 && !done[devid]) {
+static int set_smem(K kern, int bytes, DeviceOnce& done) {
+  return once_per_device(done, [&]() -> int {
     QFA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-    done[devid] = true;
-  }
-  return QFA_OK;
+    return QFA_OK;
+  });
 }
 
 template <typename T, int D, int MT>
 static int launch_fwd_sq(const ShortQDev& d, int64_t heads, cudaStream_t stream) {
   using C = SqCfg<D, MT>;
-  static bool done[64] = {};
+  static DeviceOnce done;
   int rc = set_smem(attn_fwd_shortq_kernel<T, D, MT>, C::SMEM_FWD, done);
   if (rc) return rc;
   attn_fwd_shortq_kernel<T, D, MT><<<static_cast<unsigned>(heads), C::THREADS, C::SMEM_FWD, stream>>>(d);
@@ -604,7 +604,7 @@ static int launch_fwd_sq(const ShortQDev& d, int64_t heads, cudaStream_t stream)
 template <typename T, int D, int MT>
 static int launch_bwd_sq(const ShortQDev& d, int64_t heads, cudaStream_t stream) {
   using C = SqCfg<D, MT>;
-  static bool done[64] = {};
+  static DeviceOnce done;
   int rc = set_smem(attn_bwd_shortq_kernel<T, D, MT>, C::SMEM_BWD, done);
   if (rc) return rc;
   attn_bwd_shortq_kernel<T, D, MT><<<static_cast<unsigned>(heads), C::THREADS, C::SMEM_BWD, stream>>>(d);
@@ -649,6 +649,7 @@ int attn_fwd_shortq_entry(const QfaFwdArgs& a, cudaStream_t stream) {
   d.kv = a.k; d.o = a.o; d.lse = a.lse; d.lse_stride = a.lse_stride;
   d.H = static_cast<int>(a.H); d.Sq = static_cast<int>(a.Sq); d.Skv = static_cast<int>(a.Skv); d.sm_scale = a.sm_scale;
   d.status = a.status;
+  d.epoch = next_launch_epoch();
   const int dtype = a.dtype, mt = a.Sq <= 16 ? 1 : 2;
   const int64_t D = a.D, heads = a.B * a.H;
   QFA_SQ_DISPATCH(launch_fwd_sq, d, heads, stream);
@@ -665,6 +666,7 @@ int attn_bwd_shortq_entry(const QfaBwdArgs& a, cudaStream_t stream) {
   d.dq = a.dq; d.dkv = a.dk;
   d.H = static_cast<int>(a.H); d.Sq = static_cast<int>(a.Sq); d.Skv = static_cast<int>(a.Skv); d.sm_scale = a.sm_scale;
   d.status = a.status;
+  d.epoch = next_launch_epoch();
   const int dtype = a.dtype, mt = a.Sq <= 16 ? 1 : 2;
   const int64_t D = a.D, heads = a.B * a.H;
   QFA_SQ_DISPATCH(launch_bwd_sq, d, heads, stream);

@@ -19,7 +19,6 @@ int attn_bwd_mma_entry(const QfaBwdArgs& a, float* dq_accum, cudaStream_t stream
 constexpr int64_t kStaticScratchFloats = int64_t(4) << 20;
 static __device__ __align__(256) float g_bwd_dq_scratch[kStaticScratchFloats];
 
-constexpr int kMaxDevices = 64;
 static float* g_scratch_ptr[kMaxDevices] = {};
 static std::mutex g_scratch_mutex;
 
@@ -60,9 +59,9 @@ extern "C" QFA_API int qfa_attn_bwd_static_scratch(const QfaBwdArgs* a, qfa_stre
   float* scratch = nullptr;
   int rc = scratch_for_current_device(&scratch);
   if (rc != QFA_OK) return rc;
-  // Same validation and kernels as qfa_attn_bwd, with the static array as accumulator.  The
-  // kernels' own prologue zero-fills the part of the array they use (it keeps the previous
-  // call's contents otherwise).
+  // Same validation as qfa_attn_bwd, with the static array as accumulator.  The launcher of the
+  // general backward zero-fills the part of the array the call uses with a memset on the caller's
+  // stream before its kernels run (the array keeps the previous call's contents otherwise).
   QfaBwdArgs b = *a;
   b.dq_accum = scratch;
   b.q_hat = b.k_hat = b.v_hat = nullptr;   // always the kernel that accumulates dQ in scratch memory

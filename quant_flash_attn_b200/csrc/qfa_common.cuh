@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/qfa.h"
 
 namespace qfa {
@@ -20,6 +22,29 @@ int cuda_fail(cudaError_t e, const char* what);
     cudaError_t _e = (expr);                                 \
     if (_e != cudaSuccess) return ::qfa::cuda_fail(_e, #expr); \
   } while (0)
+
+// Launch epoch for the kernels with bounded barrier waits: ONE process-wide counter for every launcher, never 0,
+// so the epoch a timed-out launch leaves in the device-side abort word is never handed out again.
+unsigned int next_launch_epoch();
+
+// One-time set-up of a kernel on the current device (opt-in shared memory size, register checks), usable from
+// several host threads at once: `setup` is idempotent, so two threads that race both run it and both succeed.
+// Devices beyond kMaxDevices are rejected instead of being launched on without the set-up.
+constexpr int kMaxDevices = 64;
+struct DeviceOnce {
+  std::atomic<bool> done[kMaxDevices];
+};
+template <typename F>
+inline int once_per_device(DeviceOnce& flags, F&& setup) {
+  int dev = 0;
+  QFA_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return cuda_fail(cudaErrorInvalidDevice, "device ordinals above 63 are not supported");
+  if (flags.done[dev].load(std::memory_order_acquire)) return QFA_OK;
+  const int rc = setup();
+  if (rc != QFA_OK) return rc;
+  flags.done[dev].store(true, std::memory_order_release);
+  return QFA_OK;
+}
 
 // ------------------------------------------------------------------ 16-bit type traits
 template <typename T>

@@ -53,6 +53,29 @@ def _check_head_dim(D: int):
         raise ValueError(f"head dimension {D} is not supported (64 or 128)")
 
 
+def _status_ptr(device) -> int:
+    """Address of the device's status word (pinned host memory the GPU writes directly).  Before handing it to
+    the next launch, report what an EARLIER launch on this device left there: a kernel whose bounded wait ran
+    out returns garbage, and the caller must hear about it even though nobody synchronised for it."""
+    _lib.raise_if_kernel_status(device)
+    return _lib.status_word(device).data_ptr()
+
+
+def _after_launch(device):
+    # QFA_CHECK_STATUS=1 (debugging aid): synchronise after every attention launch and raise at once
+    if os.environ.get("QFA_CHECK_STATUS"):
+        _lib.raise_if_kernel_status(device, synchronize=True)
+
+
+def check_kernel_status(device=None, synchronize: bool = True):
+    """Raises RuntimeError if any attention kernel launched so far on `device` (default: the current device)
+    reported a status, i.e. a bounded barrier wait inside it ran out and its outputs are invalid.  The operators
+    run this check (without synchronising) before each of their launches; call it yourself, with the default
+    `synchronize=True`, before trusting the results of the LAST launches of a run."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    _lib.raise_if_kernel_status(dev, synchronize=synchronize)
+
+
 class QuantFlashAttention(torch.autograd.Function):
     """Attention of 16-bit queries against one per-token INT8-quantized tensor used as both K and V."""
 
@@ -79,10 +102,12 @@ class QuantFlashAttention(torch.autograd.Function):
             mode=_lib.QFA_MODE_REF, dtype=_DT[q.dtype], causal=0, sm_scale=float(sm_scale),
             B=Z, H=H, Sq=N_CTX_Q, Skv=N_CTX_KV, D=HEAD_DIM,
             q=qk.data_ptr(), q_stride=_s3(qk), k=kvq, v=kvq, v_hat=None,
-            o=o.data_ptr(), o_stride=_s3(o), lse=lse.data_ptr(), lse_stride=PADDED_N_CTX_Q, status=None)
+            o=o.data_ptr(), o_stride=_s3(o), lse=lse.data_ptr(), lse_stride=PADDED_N_CTX_Q,
+            status=_status_ptr(q.device))
         with torch.cuda.device(q.device):
             rc = _lib.load().qfa_attn_fwd(C.byref(args), _stream(q))
         _lib.check(rc, "qfa_attn_fwd")
+        _after_launch(q.device)
 
         ctx.save_for_backward(qk, o, lse, kv_codes_k, kv_scale_k, kv_zp_k)
         ctx.sm_scale = sm_scale
@@ -115,9 +140,11 @@ class QuantFlashAttention(torch.autograd.Function):
                 d_o=do.data_ptr(), do_stride=sdo, lse=lse.data_ptr(), delta=delta.data_ptr(),
                 lse_stride=ctx.PADDED_N_CTX_Q,
                 dq=dq.data_ptr(), dq_stride=_s3(dq), dk=dkv.data_ptr(), dk_stride=_s3(dkv),
-                dv=None, dv_stride=_lib.c_i64x3(0, 0, 0), dq_accum=dq_accum.data_ptr(), status=None)
+                dv=None, dv_stride=_lib.c_i64x3(0, 0, 0), dq_accum=dq_accum.data_ptr(),
+                status=_status_ptr(q.device))
             rc = lib.qfa_attn_bwd(C.byref(args), stream)
         _lib.check(rc, "qfa_attn_bwd")
+        _after_launch(q.device)
         return dq, dkv, None, None
 
 
@@ -152,23 +179,17 @@ def int8_attention_forward(qq, kq, vq, causal: bool, sm_scale: float, dtype: tor
         o = torch.empty((B, H, Sq, D), dtype=dtype, device=qc.device)
     if lse is None:
         lse = torch.empty((B, H, Sq), dtype=torch.float32, device=qc.device)
-    # QFA_CHECK_STATUS=1 (debugging aid): give the kernel a status word, synchronise and raise if a bounded
-    # wait inside the kernel ran out
-    status = torch.zeros(1, dtype=torch.int32, device=qc.device) if os.environ.get("QFA_CHECK_STATUS") else None
     args = _lib.QfaFwdArgs(
         mode=_lib.QFA_MODE_INT8, dtype=_DT[dtype], causal=int(bool(causal)), sm_scale=float(sm_scale),
         B=B, H=H, Sq=Sq, Skv=Skv, D=D, q=None, q_stride=_lib.c_i64x3(0, 0, 0),
         qq=_quant_tensor(qc, qs, qz, qsum), k=_quant_tensor(kc, ks, kz, ksum), v=_quant_tensor(vc, vs, vz),
         v_hat=vhat.data_ptr() if vhat is not None else None,
         o=o.data_ptr(), o_stride=_s3(o), lse=lse.data_ptr(), lse_stride=Sq,
-        status=status.data_ptr() if status is not None else None, Hkv=Hkv)
+        status=_status_ptr(qc.device), Hkv=Hkv)
     with torch.cuda.device(qc.device):
         rc = _lib.load().qfa_attn_fwd(C.byref(args), _stream(qc))
     _lib.check(rc, "qfa_attn_fwd")
-    if status is not None:
-        code = int(status.item())
-        if code:
-            raise RuntimeError(f"qfa_attn_fwd kernel status {code}: {_lib.load().qfa_strerror(code).decode()}")
+    _after_launch(qc.device)
     return o, lse
 
 
@@ -212,7 +233,6 @@ def int8_attention_backward(qq, kq, vq, causal, sm_scale, o, lse, do, use_tc: bo
         dq_accum = torch.empty((B, H, Sq, D), dtype=torch.float32, device=dev)
     lib = _lib.load()
     stream = _stream(qc)
-    status = torch.zeros(1, dtype=torch.int32, device=dev) if os.environ.get("QFA_CHECK_STATUS") else None
     with torch.cuda.device(dev):
         so, sdo = _s3(o), _s3(do)
         rc = lib.qfa_attn_bwd_delta(o.data_ptr(), C.byref(so), do.data_ptr(), C.byref(sdo), delta.data_ptr(),
@@ -226,15 +246,12 @@ def int8_attention_backward(qq, kq, vq, causal, sm_scale, o, lse, do, use_tc: bo
             dq=dq.data_ptr(), dq_stride=_s3(dq), dk=dk.data_ptr(), dk_stride=_s3(dk),
             dv=dv.data_ptr(), dv_stride=_s3(dv),
             dq_accum=dq_accum.data_ptr() if dq_accum is not None else None,
-            status=status.data_ptr() if status is not None else None,
+            status=_status_ptr(dev),
             q_hat=q_hat.data_ptr() if use_tc else None, k_hat=k_hat.data_ptr() if use_tc else None,
             v_hat=v_hat.data_ptr() if use_tc else None)
         rc = lib.qfa_attn_bwd(C.byref(args), stream)
     _lib.check(rc, "qfa_attn_bwd")
-    if status is not None:
-        code = int(status.item())
-        if code:
-            raise RuntimeError(f"qfa_attn_bwd kernel status {code}: {lib.qfa_strerror(code).decode()}")
+    _after_launch(dev)
     return dq, dk, dv
 
 

@@ -9,7 +9,15 @@ import oracle
 
 pytestmark = pytest.mark.gpu
 
-from test_gpu_attn import HALF_ULP, REL_TOL, REL_TOL_GRAD, _close, _cpu_quant, _gen, qfa  # noqa: E402,F401
+from parity_util import close as _close, cpu_quant as _cpu_quant, gen as _gen  # noqa: E402
+
+
+@pytest.fixture(scope="module")
+def qfa():
+    import quant_flash_attn_b200 as m
+    from quant_flash_attn_b200 import _lib
+    _lib.load()
+    return m
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
@@ -30,12 +38,12 @@ def test_bshd_layout_vs_oracle(qfa, dtype, B, Sq, Skv, H, D, causal):
     qt, kt, vt = (t.transpose(1, 2).contiguous() for t in (q, k, v))
     quant = tuple(_cpu_quant(t) for t in qfa.quantize_qkv(qt.cuda(), kt.cuda(), vt.cuda()))
     o_ref, lse_ref, quant = oracle.int8_mode_forward(qt, kt, vt, causal, sm, quant=quant, round_output=False)
-    _close(o.transpose(1, 2), o_ref, what="o")
+    _close(o.transpose(1, 2), o_ref, what="bshd o")
     dq_ref, dk_ref, dv_ref = oracle.int8_mode_backward(quant, causal, sm, o.detach().transpose(1, 2).cpu(), lse_ref,
-                                                       do.transpose(1, 2), dtype, round_output=False)
-    _close(qc.grad.transpose(1, 2), dq_ref, rel=REL_TOL_GRAD[dtype], what="dq")
-    _close(kc.grad.transpose(1, 2), dk_ref, rel=REL_TOL_GRAD[dtype], what="dk")
-    _close(vc.grad.transpose(1, 2), dv_ref, rel=REL_TOL_GRAD[dtype], what="dv")
+                                                       do.transpose(1, 2), dtype, round_output=False, round_p=dtype)
+    _close(qc.grad.transpose(1, 2), dq_ref, what="bshd dq")
+    _close(kc.grad.transpose(1, 2), dk_ref, what="bshd dk")
+    _close(vc.grad.transpose(1, 2), dv_ref, what="bshd dv")
 
 
 def test_bshd_equals_bhsd_operator(qfa):

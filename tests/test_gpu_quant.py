@@ -148,6 +148,37 @@ def test_quantizer_is_idempotent_on_its_own_output(qfa):
     assert bool((err <= 0.51 * scale.float() + 0.01 * x.float().abs()).all())
 
 
+def test_quantizer_above_2_31_elements(qfa):
+    """The reference's own large case, (512, 32, 2041, 128) = 4.28e9 elements (asymmetric_quant.py:163-188; its
+    kernel needs 64-bit offsets, asymmetric_quant.py:55-61).  Checked at full size: three windows of rows (the
+    first, the one around element offset 2^31, the last) against the oracle in the documented band; the same
+    windows bit for bit against a separate launch on just that slice (small offsets); code sums and the
+    dequantization bound on every row."""
+    Z, H, M, D = 512, 32, 2041, 128
+    x = torch.empty(Z, H, M, D, device="cuda", dtype=torch.bfloat16)
+    g = torch.Generator(device="cuda").manual_seed(17)
+    for z in range(0, Z, 64):
+        x[z:z + 64].normal_(generator=g)
+    assert x.numel() > 2 ** 31
+    codes, scale, zp, rowsum = qfa.asymmetric_quant_per_token_ex(x)
+    rows_per_z = H * M
+    z_mid = (2 ** 31 // D) // rows_per_z            # the batch index whose rows straddle element offset 2^31
+    for z in (0, z_mid, Z - 1):
+        c2, s2, z2, r2 = qfa.asymmetric_quant_per_token_ex(x[z:z + 1])
+        assert torch.equal(codes[z:z + 1], c2) and torch.equal(scale[z:z + 1], s2)
+        assert torch.equal(zp[z:z + 1], z2) and torch.equal(rowsum[z:z + 1], r2)
+        sl = (slice(z, z + 1), slice(0, 2))         # 2 heads x 2041 rows per window for the CPU oracle
+        _compare_with_ieee_oracle(x[sl].float().cpu().numpy(), codes[sl], scale[sl], zp[sl], rowsum[sl])
+    for z in range(0, Z, 32):
+        sl = slice(z, z + 32)
+        c = codes[sl]
+        assert torch.equal(rowsum[sl], c.sum(-1, dtype=torch.int32))
+        sc, xf = scale[sl].float(), x[sl].float()
+        err = ((c.float() - zp[sl].float()) * sc - xf).abs()
+        assert bool((err <= 0.51 * sc + 0.01 * xf.abs()).all())
+        del c, sc, xf, err
+
+
 def test_quantizer_rejects_bad_arguments(qfa):
     with pytest.raises(RuntimeError):
         qfa.asymmetric_quant_per_token(torch.zeros(1, 1, 2, 64, dtype=torch.float16))       # CPU tensor

@@ -54,6 +54,13 @@ def test_static_scratch_backward_matches_allocating_backward():
         _lib.check(lib.qfa_attn_bwd(C.byref(args0), stream), "qfa_attn_bwd")
         dq, dk, dv = (torch.full((B, H, S, D), float("nan"), device="cuda", dtype=torch.bfloat16) for _ in range(3))
         args = _bwd_args(_lib, qq, kq, vq, o, lse, delta, do, dq, dk, dv, None, causal, sm)
+        if call == 1:
+            # dq_accum and the dequantized operands are documented as ignored: hand over buffers full of NaN and
+            # check that nothing of them reaches the result and that the caller's accumulator stays untouched
+            junk = torch.full((B, H, S, D), float("nan"), device="cuda", dtype=torch.float32)
+            junk16 = torch.full((B, H, S, D), float("nan"), device="cuda", dtype=torch.bfloat16)
+            args.dq_accum = junk.data_ptr()
+            args.q_hat = args.k_hat = args.v_hat = junk16.data_ptr()
         _lib.check(lib.qfa_attn_bwd_static_scratch(C.byref(args), stream), "qfa_attn_bwd_static_scratch")
         torch.cuda.synchronize()
         for name, got, ref in (("dq", dq, want[0]), ("dk", dk, want[1]), ("dv", dv, want[2])):
@@ -63,6 +70,8 @@ def test_static_scratch_backward_matches_allocating_backward():
             # same kernels and inputs; dq is accumulated with atomics, whose order is not fixed,
             # and delta is recomputed here in fp32 torch: allow a bf16 ulp (2^-7) of the scale
             assert err <= 2.0 ** -7 * scale, f"call {call}: {name} differs by {err} (scale {scale})"
+        if call == 1:
+            assert torch.isnan(junk).all()
 
 
 def test_static_scratch_rejects_oversized_problem():
