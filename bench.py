@@ -1,19 +1,23 @@
 #!/usr/bin/env python
 """Benchmark of the quantized-attention hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--scaling strong|weak]
     python bench.py --profile-case quant|fwd|fwd_causal|bwd|shortq     (small fixed case for a profiler capture)
 
-Workload (N=1): INT8 attention forward at B=4 H=32 S=4096 D=128, bf16 inputs ~N(0,1) with 1 % of
-the channels scaled x20, seeded, non-causal.  One step = quantize Q, K, V per token (3 launches of
-the quantizer; V also written dequantized) + one int8 attention forward.  `value` = attention ops
-4*B*H*D*S^2 per step / step time, in TOPS, inputs resident in HBM.  With N > 1 every rank runs
-the same per-GPU workload on its own heads (global batch 4*N, no collective on the data path):
-weak scaling.  Prints ONE JSON line on rank 0.
+Workload: INT8 attention forward at B=4 H=32 S=4096 D=128, bf16 inputs ~N(0,1) with 1 % of the channels scaled
+x20, seeded per (batch, head), non-causal.  One step = quantize Q, K, V per token (ONE launch of the batched
+quantizer; V is also written dequantized) + one int8 attention forward.  `value` = attention ops 4*B*H*D*S^2 of
+the WHOLE workload per step / step time, in TOPS, inputs resident in HBM.
+
+With N > 1 the 128 (batch, head) units of that fixed workload are cut into N contiguous slices, one per rank
+(128 / 64 / 32 / 16 heads per GPU at 1 / 2 / 4 / 8 GPUs), no collective on the data path: strong scaling.
+`--scaling weak` instead gives every rank the full per-GPU workload (global batch 4*N); the default run reports
+that figure too, under `extra`.  Prints ONE JSON line on rank 0.
 """
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import math
 import os
@@ -30,6 +34,8 @@ if ROOT not in sys.path:
 
 B, H, S, D = 4, 32, 4096, 128
 WORKLOAD = "int8_attn_fwd B4 H32 S4096 D128 non-causal bf16 outlier-channels (quantize q,k,v + forward)"
+METRIC = "int8_attention_forward_throughput"
+DTYPE = "int8*int8->int32 + bf16"
 
 
 def fwd_ops(b, h, sq, skv, d, causal=False):
@@ -37,18 +43,32 @@ def fwd_ops(b, h, sq, skv, d, causal=False):
     return 4 * b * h * d * pairs
 
 
-def make_inputs(b, h, s, d, device, seed_base, head0=0, dtype=torch.bfloat16):
-    """Per-(batch, head) seeded generation so that any partition of the heads sees the same data."""
+def host_threads() -> int:
+    """CPU threads this process may use (the affinity mask, not the machine's core count)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def make_heads(h0, h1, s, d, device, seed_base, kind="outlier", dtype=torch.bfloat16, tensors=3):
+    """Heads [h0, h1) of the flattened (batch x head) axis as `tensors` tensors of shape (1, h1-h0, s, d).
+    Generation is seeded per head, so any partition of the heads over ranks sees the same data."""
     out = []
-    for t in range(3):
-        x = torch.empty(b * h, s, d, dtype=dtype, device=device)
-        for i in range(b * h):
-            g = torch.Generator(device=device).manual_seed(seed_base + 1000 * t + head0 + i)
-            x[i] = torch.randn(s, d, generator=g, device=device, dtype=torch.float32).to(dtype)
-        g = torch.Generator().manual_seed(seed_base + 7 + t)
-        idx = torch.randperm(d, generator=g)[: max(1, math.ceil(0.01 * d))]
-        x[..., idx.to(device)] *= 20.0
-        out.append(x.view(b, h, s, d))
+    for t in range(tensors):
+        x = torch.empty(h1 - h0, s, d, dtype=dtype, device=device)
+        for i in range(h0, h1):
+            g = torch.Generator(device=device).manual_seed(seed_base + 1000 * t + i)
+            r = torch.randn(s, d, generator=g, device=device, dtype=torch.float32)
+            if kind == "loguniform":
+                mag = torch.empty(s, 1, device=device).uniform_(math.log(0.1), math.log(10.0), generator=g)
+                r = r * torch.exp(mag)
+            x[i - h0] = r.to(dtype)
+        if kind == "outlier":
+            g = torch.Generator().manual_seed(seed_base + 7 + t)
+            idx = torch.randperm(d, generator=g)[: max(1, math.ceil(0.01 * d))]
+            x[..., idx.to(device)] *= 20.0
+        out.append(x.view(1, h1 - h0, s, d))
     return out
 
 
@@ -161,9 +181,12 @@ def load_peaks():
 # --------------------------------------------------------------------------------------------- CPU arm
 
 def cpu_reference_sample(heads: int, s: int, d: int, repeats: int, causal=False):
-    """Times the CPU restatement of the reference math (per-token quantize -> dequantized softmax
-    attention) on `heads` heads of the workload; returns (ops per second, seconds, threads)."""
+    """Times the CPU restatement of the reference math (per-token quantize -> dequantized softmax attention) on
+    `heads` heads of the workload with every host thread this process may use; returns (ops per second, seconds,
+    threads).  The thread count is set explicitly: a launcher may have exported OMP_NUM_THREADS=1."""
     import oracle
+    threads = host_threads()
+    torch.set_num_threads(threads)
     torch.manual_seed(0)
     q, k, v = (torch.randn(1, heads, s, d).bfloat16() for _ in range(3))
     sm = 1.0 / math.sqrt(d)
@@ -176,15 +199,17 @@ def cpu_reference_sample(heads: int, s: int, d: int, repeats: int, causal=False)
 
 
 def run_reference_arm(args):
+    """The reference's math on the host cores (the oracle port; the reference itself is a set of Triton GPU
+    kernels with no CPU implementation).  Under a multi-rank launcher rank 0 alone runs it."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     heads = 2
-    # warm-up steps and timed steps each run the bounded sample once
     for _ in range(min(args.warmup, 1)):
         cpu_reference_sample(1, 1024, D, 1)
     t0 = time.perf_counter()
     ops = 0.0
+    threads = host_threads()
     for _ in range(args.steps):
         rate, dt, threads = cpu_reference_sample(heads, S, D, 1)
         ops += rate * dt
@@ -192,9 +217,9 @@ def run_reference_arm(args):
     value = ops / el / 1e12
     sample = f"{heads} of {B * H} heads of the workload per step (S={S}, D={D}), oracle port in PyTorch CPU fp32"
     line = {
-        "impl": "reference", "metric": "int8_attention_forward_throughput", "value": value, "unit": "TOPS",
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TOPS",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": el / args.steps * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8*int8->int32 + bf16",
+        "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": DTYPE,
         "data": "synthetic", "config": {"workload": WORKLOAD, "sample": sample},
         "cpu_baseline": {"value": value, "unit": "TOPS", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -202,11 +227,259 @@ def run_reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
-# --------------------------------------------------------------------------------------------- GPU arm
+# --------------------------------------------------------------------------------------------- GPU arm helpers
+
+def time_ms(fn, stream, reps=10, warm=3):
+    for _ in range(warm):
+        fn()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a.record(stream)
+    for _ in range(reps):
+        fn()
+    b.record(stream)
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / reps
+
+
+def measure_tensor_peaks(stream):
+    """tcgen05.mma issue-rate probe of the library on every SM (operands resident in shared memory, no loads, no
+    epilogue): the int8 and bf16 tensor-pipe peaks of THIS GPU, best of 5 launches each."""
+    from quant_flash_attn_b200 import _lib
+    lib = _lib.load()
+    out = {}
+    for form, n, name in ((0, 128, "int8_ss_n128"), (0, 256, "int8_ss_n256"), (1, 128, "bf16_ss_n128"),
+                          (2, 128, "bf16_ts_n128")):
+        ops = ctypes.c_double()
+        best = None
+        for _ in range(5):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            rc = lib.qfa_probe_mma_rate(form, n, 4000, ctypes.byref(ops), None, stream.cuda_stream)
+            b.record(stream)
+            torch.cuda.synchronize()
+            if rc != 0:
+                return {"error": f"qfa_probe_mma_rate returned {rc}"}
+            ms = a.elapsed_time(b)
+            best = ms if best is None else min(best, ms)
+        out[name] = ops.value / best / 1e9
+    out["how"] = ("one CTA per SM issues 16 000 tcgen05.mma (M128, K32 int8 / K16 bf16) on zeroed operand tiles "
+                  "resident in shared memory; TOPS = ops / CUDA-event time, best of 5")
+    return out
+
+
+class StepGraphs:
+    """The two launches of a step -- batched quantizer, attention forward -- each captured once into a CUDA graph
+    and replayed, so that a step costs two graph launches on the host instead of a dozen allocations and two ctypes
+    calls (at 16 heads per GPU a step is 0.2 ms of GPU time).  Falls back to eager calls if capture is refused."""
+
+    def __init__(self, qfa, q, k, v, causal, sm, stream):
+        self.qfa, self.q, self.k, self.v, self.causal, self.sm, self.stream = qfa, q, k, v, causal, sm, stream
+        self.o = torch.empty_like(q)
+        self.lse = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device)
+        self.mode = "eager"
+        self.launches_per_step = None
+        n0 = qfa.launch_count()
+        self._quant()
+        self._attn()
+        torch.cuda.synchronize()
+        self.launches_per_step = qfa.launch_count() - n0
+        try:
+            self.g_quant, self.g_attn = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.g_quant):
+                self._quant()
+            with torch.cuda.graph(self.g_attn):
+                self._attn()
+            torch.cuda.synchronize()
+            self.mode = "cuda-graph"
+        except Exception as e:        # noqa: BLE001 -- any capture problem: measure with eager launches instead
+            self.capture_error = repr(e)[:200]
+            torch.cuda.synchronize()
+
+    def _quant(self):
+        self.qq, self.kq, self.vq = self.qfa.quantize_qkv(self.q, self.k, self.v)
+
+    def _attn(self):
+        self.qfa.int8_attention_forward(self.qq, self.kq, self.vq, self.causal, self.sm, self.q.dtype, o=self.o, lse=self.lse)
+
+    def step(self, record=None):
+        if self.mode == "cuda-graph":
+            self.g_quant.replay()
+        else:
+            self._quant()
+        if record is not None:
+            record[0].record(self.stream)
+        if self.mode == "cuda-graph":
+            self.g_attn.replay()
+        else:
+            self._attn()
+        if record is not None:
+            record[1].record(self.stream)
+
+
+class RotatingRunner:
+    """Round-robin over several StepGraphs whose inputs are copies of the same data at different addresses, so
+    that the bytes touched between two uses of one copy exceed the L2 capacity and every step reads its inputs
+    from HBM even when one rank's slice of the workload would fit in L2."""
+
+    def __init__(self, runners):
+        self.runners, self.i = runners, 0
+        r0 = runners[0]
+        self.mode, self.launches_per_step = r0.mode, r0.launches_per_step
+        self.q, self.k, self.v, self.o, self.lse = r0.q, r0.k, r0.v, r0.o, r0.lse
+        self.qq, self.kq, self.vq = r0.qq, r0.kq, r0.vq
+        self.capture_error = getattr(r0, "capture_error", None)
+
+    def step(self, record=None):
+        self.runners[self.i % len(self.runners)].step(record)
+        self.i += 1
+
+
+L2_BYTES = 126e6
+
+
+def rotation_count(bytes_per_step: float) -> int:
+    """Copies needed so that a round over all of them touches at least twice the L2 capacity."""
+    return max(1, int(math.ceil(2 * L2_BYTES / max(bytes_per_step, 1.0))))
+
+
+def timed_steps(runner, steps, stream, barrier, per_step_events=True):
+    """`steps` steps bracketed by a barrier + synchronize on both sides; returns (total ms, mean ms of the attention
+    launch from per-step events, wall-clock window)."""
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    w0 = time.time()
+    t0.record(stream)
+    for i in range(steps):
+        runner.step(ev[i] if per_step_events else None)
+    t1.record(stream)
+    barrier()
+    w1 = time.time()
+    total = t0.elapsed_time(t1)
+    attn = sum(a.elapsed_time(b) for a, b in ev) / steps if per_step_events else None
+    return total, attn, (w0, w1)
+
+
+def single_gpu_extras(qfa, extra, runner, dev, stream, sm):
+    """Secondary figures measured on one GPU only (untimed region of the bench): tensor-pipe peaks, a sustained
+    run, the quantizer sweep, the sequence-length sweep, the reference's own benchmark shapes, the front end."""
+    peaks = load_peaks()
+    extra["tensor_pipe_peaks_TOPS"] = measure_tensor_peaks(stream)
+
+    # sustained: the same step back to back for >= 2 s, with the SM clock sampled meanwhile
+    sampler = ClockSampler(dev.index)
+    sampler.start()
+    n_done, t0 = 0, time.time()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    w0 = time.time()
+    a.record(stream)
+    while time.time() - t0 < 2.2:
+        for _ in range(50):
+            runner.step()
+        n_done += 50
+        torch.cuda.synchronize()
+    b.record(stream)
+    torch.cuda.synchronize()
+    w1 = time.time()
+    sampler.window(w0, w1)
+    ck = sampler.stop()
+    s_ms = a.elapsed_time(b) / n_done
+    tops = fwd_ops(1, runner.q.shape[1], S, S, D) / s_ms / 1e9
+    extra["sustained"] = {"seconds": w1 - w0, "steps": n_done, "ms_per_step": s_ms, "TOPS": tops,
+                          "sm_mhz_median": ck.get("sm_mhz"), "sm_max_mhz": ck.get("sm_max_mhz"),
+                          "reasons": ck.get("reasons"),
+                          "TOPS_at_max_clock": (tops * ck["sm_max_mhz"] / ck["sm_mhz"]) if ck.get("sm_mhz") and ck.get("sm_max_mhz") else None,
+                          "frac_of_bf16_sustained_" + peaks["source"]: tops / peaks["bf16_tflops_sustained"]}
+
+    # quantizer: [N tokens x D] bf16, N from 64 Ki to 16 Mi, D = 64 / 128; rotating buffers so that every launch
+    # reads from HBM even where one tensor would fit the 126 MB L2
+    sweep = []
+    for d in (64, 128):
+        for n_tok in (1 << 16, 1 << 18, 1 << 20, 1 << 22, 1 << 24):
+            bytes_in = n_tok * d * 2
+            n_buf = max(1, min(8, int(math.ceil(512e6 / bytes_in))))
+            xs = [torch.randn(1, 1, n_tok, d, device=dev, dtype=torch.bfloat16) for _ in range(n_buf)]
+            it = [0]
+
+            def qstep():
+                qfa.asymmetric_quant_per_token_ex(xs[it[0] % n_buf])
+                it[0] += 1
+            ms = time_ms(qstep, stream, reps=max(5, 2 * n_buf), warm=n_buf)
+            byt = n_tok * (2 * d + d + 2 + 1 + 4)
+            sweep.append({"tokens": n_tok, "D": d, "ms": ms, "GBps": byt / ms / 1e6,
+                          "frac_of_hbm_" + peaks["source"]: byt / ms / 1e6 / peaks["hbm_gbs"], "buffers": n_buf})
+            del xs
+    extra["quantizer_sweep"] = sweep
+    big = max((r for r in sweep if r["D"] == 128 and r["tokens"] == 1 << 20), key=lambda r: r["GBps"])
+    extra["quantizer"] = {"tokens": big["tokens"], "D": 128, "ms": big["ms"], "GBps": big["GBps"],
+                          "bytes_per_token": 2 * D + D + 7,
+                          "frac_of_hbm_" + peaks["source"]: big["GBps"] / peaks["hbm_gbs"]}
+
+    # sequence-length sweep: B*S = 32768, H = 16, D = 128, causal, forward + backward (3.5 x forward ops)
+    seq = []
+    for s_len in (512, 1024, 2048, 4096, 8192, 16384):
+        b_ = 32768 // s_len
+        tq, tk, tv, tdo = (t.view(b_, 16, s_len, D) for t in make_heads(0, b_ * 16, s_len, D, dev, 500 + s_len, "normal", tensors=4))
+        qq, kq, vq = qfa.quantize_qkv(tq, tk, tv)
+        o_, lse_ = qfa.int8_attention_forward(qq, kq, vq, True, sm, torch.bfloat16)
+        f_ms = time_ms(lambda: qfa.int8_attention_forward(qq, kq, vq, True, sm, torch.bfloat16), stream, reps=5)
+        b_ms = time_ms(lambda: qfa.int8_attention_backward(qq, kq, vq, True, sm, o_, lse_, tdo), stream, reps=5)
+        fo = fwd_ops(b_, 16, s_len, s_len, D, True)
+        seq.append({"S": s_len, "B": b_, "fwd_ms": f_ms, "bwd_ms": b_ms, "fwd_TOPS": fo / f_ms / 1e9,
+                    "fwd_bwd_TOPS": 3.5 * fo / (f_ms + b_ms) / 1e9})
+        del tq, tk, tv, tdo, qq, kq, vq, o_, lse_
+    extra["seq_sweep_BS32768_H16_D128_causal"] = seq
+
+    # training shape: B8 H16 S2048 D64 causal through the autograd operator (quantization included)
+    tb, th, ts, td = 8, 16, 2048, 64
+    tq, tk, tv, tdo = (t.view(tb, th, ts, td) for t in make_heads(0, tb * th, ts, td, dev, 99, "normal", tensors=4))
+    tsm = 1.0 / math.sqrt(td)
+
+    def train_step():
+        a_, b2, c = (t.detach().requires_grad_() for t in (tq, tk, tv))
+        qfa.quant_attention(a_, b2, c, True, tsm).backward(tdo)
+    t_ms = time_ms(train_step, stream, reps=5)
+    extra["fwd_bwd_B8H16S2048D64_causal"] = {"ms": t_ms, "TOPS": 3.5 * fwd_ops(tb, th, ts, ts, td, True) / t_ms / 1e9}
+    del tq, tk, tv, tdo
+
+    # flash_attn_func-style front end: the headline workload handed over in (B,S,H,D) memory
+    fq, fk, fv = (t.view(B, H, S, D).transpose(1, 2).contiguous() for t in (runner.q, runner.k, runner.v))
+    fe_ms = time_ms(lambda: qfa.quant_flash_attn_func(fq, fk, fv, causal=False, softmax_scale=sm), stream, reps=5)
+    extra["frontend_bshd_B4S4096H32D128"] = {"ms": fe_ms, "TOPS": fwd_ops(B, H, S, S, D) / fe_ms / 1e9}
+    del fq, fk, fv
+
+    # the reference's own benchmark regime (test_speed.py:45,56-59; compute_flops.py:94-96): fp16 queries of 16 rows
+    # against a long per-token-quantized K=V, ref mode, forward and backward.  HBM-bound on the int8 codes:
+    # algorithmic bytes = NKV * (D + 3) per head read once (+ Q, O), reported against the measured copy bandwidth
+    sq = []
+    for (z, hh, nq, nkv, dd) in ((256, 16, 16, 1024, 128), (256, 16, 16, 4096, 128), (64, 16, 16, 4096, 64)):
+        rq = torch.randn(z, hh, nq, dd, device=dev, dtype=torch.float16, requires_grad=True)
+        rkv = torch.randn(z, hh, nkv, dd, device=dev, dtype=torch.float16, requires_grad=True)
+        go = torch.randn_like(rq)
+        kvq = qfa.asymmetric_quant_per_token(rkv.detach())
+        rsm = 1.0 / math.sqrt(dd)
+        with torch.no_grad():
+            f_ms = time_ms(lambda: qfa.quant_flash_attn(rq, rkv, kvq, rsm), stream, reps=10)
+
+        def fb():
+            rq.grad = None
+            rkv.grad = None
+            qfa.quant_flash_attn(rq, rkv, kvq, rsm).backward(go)
+        fb_ms = time_ms(fb, stream, reps=5)
+        byt = z * hh * (nkv * (dd + 3) + 2 * nq * dd * 2)
+        sq.append({"Z": z, "H": hh, "NQ": nq, "NKV": nkv, "D": dd, "fwd_ms": f_ms, "fwd_bwd_ms": fb_ms,
+                   "fwd_TFLOPs": 4.0 * z * hh * nq * nkv * dd / f_ms / 1e9, "fwd_GBps": byt / f_ms / 1e6,
+                   "fwd_frac_of_hbm_" + peaks["source"]: byt / f_ms / 1e6 / peaks["hbm_gbs"]})
+        del rq, rkv, go, kvq
+    extra["short_query_ref_mode"] = sq
+
 
 def run_ours(args):
     import torch.distributed as dist
     import quant_flash_attn_b200 as qfa
+    from quant_flash_attn_b200 import shard_bounds
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -223,120 +496,120 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    def max_over_ranks(*vals):
+        if world == 1:
+            return list(vals)
+        t = torch.tensor(vals, device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.tolist()
+
     sm = 1.0 / math.sqrt(D)
-    # every rank owns B*H heads of a global batch of B*world
-    q, k, v = make_inputs(B, H, S, D, dev, seed_base=1234, head0=rank * B * H)
-    ops_step = fwd_ops(B, H, S, S, D, False)
     stream = torch.cuda.current_stream()
+    n_units = B * H
+    weak = args.scaling == "weak"
+    if weak:                       # every rank owns B*H heads of a global batch of B*world
+        h0, h1, total_units = rank * n_units, (rank + 1) * n_units, n_units * world
+    else:                          # the fixed B*H heads are cut into contiguous slices
+        (h0, h1), total_units = shard_bounds(n_units, world, rank), n_units
+    q, k, v = make_heads(h0, h1, S, D, dev, seed_base=1234)
+    ops_total = fwd_ops(1, total_units, S, S, D, False)
+    ops_local = fwd_ops(1, h1 - h0, S, S, D, False)
 
-    o = torch.empty_like(q)
-    lse = torch.empty(B, H, S, dtype=torch.float32, device=dev)
-
-    def step(record=None):
-        qq, kq, vq = qfa.quantize_qkv(q, k, v)
-        if record is not None:
-            record[0].record(stream)
-        qfa.int8_attention_forward(qq, kq, vq, False, sm, torch.bfloat16, o=o, lse=lse)
-        if record is not None:
-            record[1].record(stream)
-
+    in_bytes = 3 * q.numel() * q.element_size()
+    n_rot = rotation_count(in_bytes)
+    runner = RotatingRunner([StepGraphs(qfa, q, k, v, False, sm, stream)] +
+                            [StepGraphs(qfa, q.clone(), k.clone(), v.clone(), False, sm, stream) for _ in range(n_rot - 1)])
     for _ in range(max(args.warmup, 3)):
-        step()
+        runner.step()
     barrier()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-        for _ in range(20):           # let nvidia-smi come up (it takes a few hundred ms) while the GPU stays busy
-            step()
+    # keep every GPU busy for a few hundred milliseconds before the timed region: the clock sampler comes up and
+    # the clocks settle where a long run holds them
+    t_spin = time.time()
+    while time.time() - t_spin < 0.4:
+        for _ in range(20):
+            runner.step()
         torch.cuda.synchronize()
-    launches0 = qfa.launch_count()
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    wall0 = time.time()
-    t_begin.record(stream)
-    for i in range(args.steps):
-        step(ev[i])
-    t_end.record(stream)
-    barrier()
-    wall1 = time.time()
+    ms_total, attn_ms, (wall0, wall1) = timed_steps(runner, args.steps, stream, barrier)
+    qfa.check_kernel_status()
     if rank == 0:
         sampler.window(wall0, wall1)
-    launches = qfa.launch_count() - launches0
-    ms_total = t_begin.elapsed_time(t_end)
-    attn_ms = sum(a.elapsed_time(b) for a, b in ev) / args.steps
-    if world > 1:
-        t = torch.tensor([ms_total, attn_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total, attn_ms = t.tolist()
+    ms_total, attn_ms_max = max_over_ranks(ms_total, attn_ms)
     clocks = sampler.stop() if rank == 0 else None
     ms_step = ms_total / args.steps
-    value = ops_step * world / (ms_step * 1e-3) / 1e12
+    value = ops_total / (ms_step * 1e-3) / 1e12
+    launches = runner.launches_per_step * args.steps
 
-    # ---- secondary figures (rank-local, untimed region): quantizer GB/s, causal forward, fwd+bwd
-    def time_ms(fn, reps=10, warm=3):
-        for _ in range(warm):
-            fn()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        a.record(stream)
-        for _ in range(reps):
-            fn()
-        b.record(stream)
-        torch.cuda.synchronize()
-        return a.elapsed_time(b) / reps
+    extra = {"launch_mode": runner.mode, "heads_per_gpu": h1 - h0, "rotating_input_copies": n_rot, "attn_ms_rank0": attn_ms,
+             "attn_ms_max_over_ranks": attn_ms_max}
+    if runner.mode != "cuda-graph":
+        extra["graph_capture_error"] = getattr(runner, "capture_error", None)
 
-    extra = {}
-    if rank == 0:
-        n_tok = B * H * S
-        big = torch.randn(8, 32, 4096, D, device=dev, dtype=torch.bfloat16)   # 268 MB in: larger than L2
-        q_ms = time_ms(lambda: qfa.asymmetric_quant_per_token_ex(big))
-        q_bytes = big.numel() // D * (2 * D + D + 2 + 1 + 4)
-        extra["quantizer"] = {"tokens": big.numel() // D, "D": D, "ms": q_ms, "GBps": q_bytes / q_ms / 1e6,
-                              "bytes_per_token": 2 * D + D + 7}
-        del big
-        qq, kq, vq = qfa.quantize_qkv(q, k, v)
-        c_ms = time_ms(lambda: qfa.int8_attention_forward(qq, kq, vq, True, sm, torch.bfloat16, o=o, lse=lse))
-        extra["fwd_causal"] = {"ms": c_ms, "TOPS": fwd_ops(B, H, S, S, D, True) / c_ms / 1e9}
-        n_ms = time_ms(lambda: qfa.int8_attention_forward(qq, kq, vq, False, sm, torch.bfloat16, o=o, lse=lse))
-        extra["fwd_noncausal_kernel"] = {"ms": n_ms, "TOPS": ops_step / n_ms / 1e9}
-        # forward + backward at the headline shape (ops = 3.5 x forward, test_speed.py:114-116)
-        hdo = torch.randn_like(q)
+    # ---- the other figures the metric names, on the same partition, max over ranks: causal forward, fwd+bwd
+    def partition_extras():
+        out = {}
+        qq, kq, vq = runner.qq, runner.kq, runner.vq
+        do = make_heads(h0, h1, S, D, dev, seed_base=4321, kind="normal", tensors=1)[0]
         for causal in (False, True):
-            ho, hlse = qfa.int8_attention_forward(qq, kq, vq, causal, sm, torch.bfloat16)
-            f_ms = time_ms(lambda: qfa.int8_attention_forward(qq, kq, vq, causal, sm, torch.bfloat16, o=o, lse=lse), reps=5)
-            b_ms = time_ms(lambda: qfa.int8_attention_backward(qq, kq, vq, causal, sm, ho, hlse, hdo), reps=5)
-            fo = fwd_ops(B, H, S, S, D, causal)
-            extra["fwd_bwd_B4H32S4096D128_" + ("causal" if causal else "noncausal")] = {
-                "fwd_ms": f_ms, "bwd_ms": b_ms, "bwd_TOPS": 2.5 * fo / b_ms / 1e9, "TOPS": 3.5 * fo / (f_ms + b_ms) / 1e9}
-        del hdo, ho, hlse
-        # flash_attn_func-style front end: the same workload handed over in (B,S,H,D) memory; quantization and
-        # attention read and write through strides, so this should cost what the timed step costs
-        fq, fk, fv = (t.transpose(1, 2).contiguous() for t in (q, k, v))
-        fe_ms = time_ms(lambda: qfa.quant_flash_attn_func(fq, fk, fv, causal=False, softmax_scale=sm), reps=5)
-        extra["frontend_bshd_B4S4096H32D128"] = {"ms": fe_ms, "TOPS": ops_step / fe_ms / 1e9}
-        del fq, fk, fv
-        # training shape: B8 H16 S2048 D64 causal, forward + backward (ops = 3.5 x forward)
-        tb, th, ts, td = 8, 16, 2048, 64
-        tq, tk, tv = make_inputs(tb, th, ts, td, dev, seed_base=99)
-        tdo = torch.randn_like(tq)
-        tsm = 1.0 / math.sqrt(td)
+            tag = "causal" if causal else "noncausal"
+            o_, lse_ = qfa.int8_attention_forward(qq, kq, vq, causal, sm, torch.bfloat16)
+            f_ms = time_ms(lambda: qfa.int8_attention_forward(qq, kq, vq, causal, sm, torch.bfloat16, o=runner.o,
+                                                              lse=runner.lse), stream, reps=5)
+            b_ms = time_ms(lambda: qfa.int8_attention_backward(qq, kq, vq, causal, sm, o_, lse_, do), stream, reps=5)
+            barrier()
+            f_ms, b_ms = max_over_ranks(f_ms, b_ms)
+            fo = fwd_ops(1, total_units, S, S, D, causal)
+            out["fwd_" + tag] = {"ms": f_ms, "TOPS": fo / f_ms / 1e9}
+            out["fwd_bwd_" + tag] = {"fwd_ms": f_ms, "bwd_ms": b_ms, "bwd_TOPS": 2.5 * fo / b_ms / 1e9,
+                                     "TOPS": 3.5 * fo / (f_ms + b_ms) / 1e9}
+            del o_, lse_
+        return out
 
-        def train_step():
-            a, b_, c = (t.detach().requires_grad_() for t in (tq, tk, tv))
-            out = qfa.quant_attention(a, b_, c, True, tsm)
-            out.backward(tdo)
-        t_ms = time_ms(train_step, reps=5)
-        extra["fwd_bwd_B8H16S2048D64_causal"] = {"ms": t_ms, "TOPS": 3.5 * fwd_ops(tb, th, ts, ts, td, True) / t_ms / 1e9}
-        del tq, tk, tv, tdo
+    extra["B4H32S4096D128_partitioned"] = partition_extras()
+
+    # ---- long context: B1 H32 S32768 D128 causal, log-uniform token magnitudes, its 32 heads partitioned
+    def long_context():
+        c_h0, c_h1 = (rank * 32, rank * 32 + 32) if weak else shard_bounds(32, world, rank)
+        if c_h1 <= c_h0:
+            ms = 0.0
+        else:
+            cq, ck, cv = make_heads(c_h0, c_h1, 32768, D, dev, seed_base=77, kind="loguniform")
+            cqq, ckq, cvq = qfa.quantize_qkv(cq, ck, cv)
+            del cq, ck, cv
+            ms = time_ms(lambda: qfa.int8_attention_forward(cqq, ckq, cvq, True, sm, torch.bfloat16), stream, reps=3, warm=1)
+        barrier()
+        (ms,) = max_over_ranks(ms)
+        heads = 32 * world if weak else 32
+        return {"ms": ms, "TOPS": fwd_ops(1, heads, 32768, 32768, D, True) / ms / 1e9, "heads_total": heads}
+
+    extra["long_context_B1H32S32768D128_causal_fwd"] = long_context()
+
+    # ---- with N > 1 also the other scaling mode: every rank runs the full per-GPU workload (replicas)
+    if world > 1 and not weak:
+        fq, fk, fv = make_heads(rank * n_units, (rank + 1) * n_units, S, D, dev, seed_base=1234)
+        rep = StepGraphs(qfa, fq, fk, fv, False, sm, stream)        # 403 MB of inputs per step: larger than L2
+        for _ in range(3):
+            rep.step()
+        r_total, _, _ = timed_steps(rep, max(5, min(args.steps, 20)), stream, barrier, per_step_events=False)
+        (r_total,) = max_over_ranks(r_total)
+        r_step = r_total / max(5, min(args.steps, 20))
+        extra["weak_scaling_replicas"] = {"ms_per_step": r_step, "global_batch": B * world,
+                                          "TOPS": fwd_ops(B * world, H, S, S, D) / r_step / 1e9}
+        del rep, fq, fk, fv
+
+    if rank == 0 and world == 1:
+        single_gpu_extras(qfa, extra, runner, dev, stream, sm)
 
     # ---- end to end through the public host-tensor operator: pinned host q, k, v in, pinned host o out, every
-    # step; the operator cuts the heads into slices and overlaps their copies with the kernels
+    # step; the operator cuts the heads into slices and overlaps their copies with the kernels.  Each rank moves
+    # only its own heads.
     hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
     ho = torch.empty(q.shape, dtype=q.dtype).pin_memory()
 
     def e2e_step():
-        qfa.quant_attention_host(hq, hk, hv, False, sm, out=ho, device=dev)
+        qfa.quant_attention_host(hq, hk, hv, False, sm, out=ho, device=dev, slices=min(16, h1 - h0))
 
     e2e_steps = max(3, min(args.steps, 10))
     for _ in range(2):
@@ -348,51 +621,74 @@ def run_ours(args):
         e2e_step()
     b_.record(stream)
     barrier()
-    e2e_ms = a.elapsed_time(b_) / e2e_steps
-    if world > 1:
-        t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = t.item()
-    e2e = {"value": ops_step * world / (e2e_ms * 1e-3) / 1e12, "unit": "TOPS",
-           "h2d_bytes_per_step": 3 * q.numel() * q.element_size(), "d2h_bytes_per_step": q.numel() * q.element_size(),
-           "ms_per_step": e2e_ms, "steps": e2e_steps}
+    (e2e_ms,) = max_over_ranks(a.elapsed_time(b_) / e2e_steps)
+    qfa.check_kernel_status()
+    # bytes of the WHOLE job per step (all ranks), counted from the tensors that are copied
+    frac = total_units / (h1 - h0)
+    e2e = {"value": ops_total / (e2e_ms * 1e-3) / 1e12, "unit": "TOPS",
+           "h2d_bytes_per_step": int(3 * q.numel() * q.element_size() * frac),
+           "d2h_bytes_per_step": int(q.numel() * q.element_size() * frac),
+           "ms_per_step": e2e_ms, "steps": e2e_steps,
+           "per_rank_h2d_GBps": 3 * q.numel() * q.element_size() / e2e_ms / 1e6}
 
     if rank == 0:
-        peaks = load_peaks()
-        long_run = ms_total > 2000.0
-        peak = peaks["bf16_tflops_sustained"] if long_run else peaks["bf16_tflops"]
-        achieved = ops_step / (attn_ms * 1e-3) / 1e12
-        roofline = {
-            "bound": "tensor", "kernel": "int8 attention forward", "achieved": achieved, "peak": peak,
-            "unit": "TFLOP/s", "frac": achieved / peak,
-            "peak_kind": ("sustained" if long_run else "burst") + " bf16 dense, of " + peaks["source"],
-            "frac_of_mixed_int8_bf16": achieved / (1.0 / (0.5 / (2 * peak) + 0.5 / peak)),
-            "frac_of_int8_nominal_4500": achieved / 4500.0,
-            # DRAM bytes per launch: one profiler capture of the same kernel at B1 H16 (the full workload is too large
-            # to capture) read 34.55 MB + wrote 0.22 MB for 16 heads; K, V^ and Q are read once per head and O
-            # (134 MB at full size, written once) was still in L2 when that small kernel ended, so the figure is
-            # per-head reads scaled by the heads of a launch plus the output bytes
-            "traffic": (B * H) * (34.55e6 / 16) + B * H * S * D * 2,
-            "traffic_note": "scaled from a 16-head capture: 2.16 MB read per head + output bytes",
-            "ms_per_launch": attn_ms,
-        }
-        if "quantizer" in extra:
-            extra["quantizer"]["frac_of_hbm_" + peaks["source"]] = extra["quantizer"]["GBps"] / peaks["hbm_gbs"]
+        print(json.dumps(result_line(args, world, value, ms_step, ms_total, attn_ms, ops_local, launches, clocks, e2e,
+                                     extra, weak, h1 - h0)), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def result_line(args, world, value, ms_step, ms_total, attn_ms, ops_local, launches, clocks, e2e, extra, weak, n_local):
+    peaks = load_peaks()
+    long_run = ms_total > 2000.0
+    peak = peaks["bf16_tflops_sustained"] if long_run else peaks["bf16_tflops"]
+    achieved = ops_local / (attn_ms * 1e-3) / 1e12
+    tp = extra.get("tensor_pipe_peaks_TOPS", {})
+    roofline = {
+        "bound": "tensor", "kernel": "attn_fwd_tc_kernel (int8 attention forward, rank 0's launch)",
+        "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+        "peak_kind": ("sustained" if long_run else "burst") + " bf16 dense (library GEMM), of " + peaks["source"],
+        "frac_of_int8_nominal_4500": achieved / 4500.0,
+        # DRAM bytes per launch: one profiler capture of the same kernel at B1 H16 (the full workload is too large
+        # to capture) read 34.55 MB + wrote 0.22 MB for 16 heads; K, V^ and Q are read once per head and O (written
+        # once) was still in L2 when that small kernel ended, so the figure is per-head reads scaled by the heads
+        # of a launch plus the output bytes
+        "traffic": n_local * (34.55e6 / 16) + n_local * S * D * 2,
+        "traffic_note": "scaled from a 16-head capture: 2.16 MB read per head + output bytes",
+        "ms_per_launch": attn_ms,
+    }
+    if "int8_ss_n128" in tp:
+        # half of the forward's operations run as int8 MMAs (Q.K^T), half as bf16 MMAs (P.V): the time both need at
+        # the probe's measured issue rates is the tensor-pipe floor of the kernel
+        i8, bf = tp["int8_ss_n128"], tp["bf16_ts_n128"]
+        roofline["peak_int8_measured"] = i8
+        roofline["peak_bf16_mma_measured"] = bf
+        roofline["frac_of_int8_measured"] = achieved / i8
+        roofline["frac_of_mixed_int8_bf16_measured"] = achieved * (0.5 / i8 + 0.5 / bf)
+    else:
+        roofline["frac_of_mixed_int8_bf16"] = achieved / (1.0 / (0.5 / (2 * peak) + 0.5 / peak))
+    cpu_baseline = None
+    if world == 1:
         cpu_rate, cpu_dt, threads = cpu_reference_sample(2, S, D, 2)
         cpu_baseline = {"value": cpu_rate / 1e12, "unit": "TOPS", "cores": threads, "kind": "port",
                         "sample": f"2 of {B * H} heads (S={S}, D={D}) x2 repeats, {cpu_dt:.1f} s, PyTorch CPU fp32 oracle"}
-        line = {
-            "metric": "int8_attention_forward_throughput", "value": value, "unit": "TOPS", "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "int8*int8->int32 + bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "global_batch": B * world, "heads": H, "seq_len": S, "head_dim": D,
-                       "partition": f"heads x{world}", "l2": "inputs (3 x 134 MB) larger than the 126 MB L2"},
-            "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches,
-            "clocks": clocks, "extra": extra,
-        }
-        print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    line = {
+        "metric": METRIC, "value": value, "unit": "TOPS", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "weak" if weak else "strong", "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
+        "config": {"workload": WORKLOAD, "global_batch": B * world if weak else B, "heads": H, "seq_len": S,
+                   "head_dim": D,
+                   "partition": (f"replicas: B4 H32 on each of {world} GPUs" if weak else
+                                 f"{B * H} (batch x head) units cut into {world} contiguous slices, {n_local} per GPU"),
+                   "l2": f"inputs larger than L2: a step reads {3 * n_local * S * D * 2 / 1e6:.0f} MB of q, k, v per GPU and "
+                         f"the steps rotate over {extra.get('rotating_input_copies')} copies of them at different "
+                         "addresses (>= 252 MB touched between two uses of a copy; L2 is 126 MB)",
+                   "launch": extra.get("launch_mode")},
+        "roofline": roofline, "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "extra": extra,
+    }
+    if cpu_baseline is not None:
+        line["cpu_baseline"] = cpu_baseline
+    return line
 
 
 def run_profile_case(case: str):
@@ -444,6 +740,8 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
+                    help="with --gpus N > 1: partition the fixed workload (strong) or replicate it per GPU (weak)")
     ap.add_argument("--profile-case", default=None, choices=["quant", "fwd", "fwd_causal", "bwd", "shortq"])
     args = ap.parse_args()
     if args.profile_case:

@@ -77,6 +77,24 @@ QFA_API int qfa_quant_dequant_per_token(const void* x, int8_t* codes, uint16_t* 
                                 int64_t sx_z, int64_t sx_h, int64_t sx_m, int64_t sx_k,
                                 int dtype, qfa_stream_t stream);
 
+/* Several tensors in one call.  Replaces the back-to-back asymmetric_quant_per_token calls a caller of the
+ * attention path makes for its operands (the reference quantizes outside the attention operator,
+ * test_accuracy.py:88; the int8 operator needs Q, K and V).  Each job has the arguments of
+ * qfa_quant_dequant_per_token.  At most 4 jobs; when all of them have the same head dimension, inner stride 1
+ * and 16-byte aligned rows they run as ONE kernel launch (block ranges of one grid), otherwise one launch per
+ * job; results are bit-identical to separate calls either way. */
+typedef struct {
+  const void* x;
+  int8_t* codes;
+  uint16_t* scale_f16;
+  int8_t* zp;
+  int32_t* rowsum_or_null;
+  void* dequant_or_null;
+  int64_t Z, H, M, D;
+  int64_t sx_z, sx_h, sx_m, sx_k;
+} QfaQuantJob;
+QFA_API int qfa_quant_batch_per_token(const QfaQuantJob* jobs, int n_jobs, int dtype, qfa_stream_t stream);
+
 /* Dequantize: out[token][:] = (code - zp) * fp16(scale) rounded to `dtype`, the operand the reference
  * builds at quant_flash_attn.py:65-66 / :150-151.  codes (Z,H,M,D) with element strides s_z, s_h, s_m (inner
  * stride 1, D a multiple of 16); scale / zp contiguous over tokens; out contiguous (Z,H,M,D). */
@@ -209,6 +227,16 @@ QFA_API int64_t qfa_static_scratch_capacity(void);
  * launches of every entry point are unaffected.  Lets a deployment check the time-out reporting path end to
  * end without provoking a fault. */
 QFA_API int qfa_selftest_wait_timeout(uint64_t budget_ns, int32_t* status, qfa_stream_t stream);
+
+/* Tensor-pipe rate probe.  No counterpart in the reference.  One CTA per SM of the current device issues
+ * `iters` (2 .. 20000) rounds of four K-steps of 128 x n x K tcgen05 MMAs on operand tiles resident in shared
+ * memory (no loads, no epilogue), so that ops / time is the peak rate of that MMA form on this GPU: the
+ * denominator the attention kernels' int8 roofline needs and no library GEMM reports.
+ *   form 0: kind::i8, A and B from shared memory (K = 32)      form 1: kind::f16 (bf16), A and B from shared memory
+ *   form 2: kind::f16 (bf16), A from tensor memory             (K = 16);   n = 128 or 256.
+ * *ops_out (host pointer, may be NULL) receives 2 * 128 * n * K * 4 * iters * SMs; time the launch with events on
+ * `stream`.  `status` as for the attention kernels (may be NULL). */
+QFA_API int qfa_probe_mma_rate(int form, int n, int iters, double* ops_out, int32_t* status, qfa_stream_t stream);
 
 /* Text for a return / status code. */
 QFA_API const char* qfa_strerror(int code);

@@ -23,6 +23,13 @@ class QfaQuantTensor(C.Structure):
                 ("zp", C.c_void_p), ("rowsum", C.c_void_p)]
 
 
+class QfaQuantJob(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("codes", C.c_void_p), ("scale_f16", C.c_void_p), ("zp", C.c_void_p),
+                ("rowsum_or_null", C.c_void_p), ("dequant_or_null", C.c_void_p),
+                ("Z", C.c_int64), ("H", C.c_int64), ("M", C.c_int64), ("D", C.c_int64),
+                ("sx_z", C.c_int64), ("sx_h", C.c_int64), ("sx_m", C.c_int64), ("sx_k", C.c_int64)]
+
+
 class QfaFwdArgs(C.Structure):
     _fields_ = [("mode", C.c_int32), ("dtype", C.c_int32), ("causal", C.c_int32), ("sm_scale", C.c_float),
                 ("B", C.c_int64), ("H", C.c_int64), ("Sq", C.c_int64), ("Skv", C.c_int64), ("D", C.c_int64),
@@ -52,6 +59,7 @@ _I64 = C.c_int64
 SIGNATURES = {
     "qfa_quant_per_token": (C.c_int, [C.c_void_p] * 5 + [_I64] * 8 + [C.c_int, C.c_void_p]),
     "qfa_quant_dequant_per_token": (C.c_int, [C.c_void_p] * 6 + [_I64] * 8 + [C.c_int, C.c_void_p]),
+    "qfa_quant_batch_per_token": (C.c_int, [C.POINTER(QfaQuantJob), C.c_int, C.c_int, C.c_void_p]),
     "qfa_dequant_per_token": (C.c_int, [C.c_void_p] * 4 + [_I64] * 7 + [C.c_int, C.c_void_p]),
     "qfa_attn_fwd": (C.c_int, [C.POINTER(QfaFwdArgs), C.c_void_p]),
     "qfa_attn_bwd_delta": (C.c_int, [C.c_void_p, C.POINTER(c_i64x3), C.c_void_p, C.POINTER(c_i64x3), C.c_void_p,
@@ -60,6 +68,7 @@ SIGNATURES = {
     "qfa_attn_bwd_static_scratch": (C.c_int, [C.POINTER(QfaBwdArgs), C.c_void_p]),
     "qfa_static_scratch_capacity": (C.c_int64, []),
     "qfa_selftest_wait_timeout": (C.c_int, [C.c_uint64, C.c_void_p, C.c_void_p]),
+    "qfa_probe_mma_rate": (C.c_int, [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_double), C.c_void_p, C.c_void_p]),
     "qfa_strerror": (C.c_char_p, [C.c_int]),
     "qfa_last_cuda_error": (C.c_char_p, []),
     "qfa_version": (C.c_int, []),

@@ -12,7 +12,7 @@ import sys
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libqfa_sm100a.so")
-SOURCES = ["api.cu", "quantize.cu", "attn_fwd_mma.cu", "attn_fwd_tc.cu", "attn_bwd_mma.cu", "attn_bwd_tc.cu", "attn_shortq.cu", "no_alloc.cu"]
+SOURCES = ["api.cu", "quantize.cu", "attn_fwd_mma.cu", "attn_fwd_tc.cu", "attn_bwd_mma.cu", "attn_bwd_tc.cu", "attn_shortq.cu", "no_alloc.cu", "mma_probe.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",

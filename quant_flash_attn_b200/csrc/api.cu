@@ -27,6 +27,7 @@ int cuda_fail(cudaError_t e, const char* what) {
 int quant_entry(const void* x, int8_t* codes, uint16_t* scale, int8_t* zp, int32_t* rowsum, void* dequant, int64_t Z,
                 int64_t H, int64_t M, int64_t D, int64_t sz, int64_t sh, int64_t sm, int64_t sk, int dtype,
                 cudaStream_t stream);
+int quant_batch_entry(const QfaQuantJob* jobs, int n, int dtype, cudaStream_t stream);
 int dequant_entry(const int8_t* codes, const uint16_t* scale, const int8_t* zp, void* out, int64_t Z, int64_t H, int64_t M,
                   int64_t D, int64_t sz, int64_t sh, int64_t sm, int dtype, cudaStream_t stream);
 int attn_bwd_tc_supported(const QfaBwdArgs& a);
@@ -35,6 +36,7 @@ int attn_fwd_mma_entry(const QfaFwdArgs& a, cudaStream_t stream);
 int attn_fwd_tc_supported(const QfaFwdArgs& a);
 int attn_fwd_tc_entry(const QfaFwdArgs& a, cudaStream_t stream);
 int attn_bwd_mma_entry(const QfaBwdArgs& a, float* dq_accum, cudaStream_t stream);
+int mma_probe_entry(int form, int n, int iters, double* ops_out, int32_t* status, cudaStream_t stream);
 int wait_timeout_selftest_entry(uint64_t budget_ns, int32_t* status, cudaStream_t stream);
 int attn_fwd_shortq_supported(const QfaFwdArgs& a);
 int attn_fwd_shortq_entry(const QfaFwdArgs& a, cudaStream_t stream);
@@ -81,6 +83,10 @@ QFA_API int qfa_quant_dequant_per_token(const void* x, int8_t* codes, uint16_t* 
                                 int64_t sx_h, int64_t sx_m, int64_t sx_k, int dtype, qfa_stream_t stream) {
   return quant_entry(x, codes, scale_f16, zp, rowsum_or_null, dequant_or_null, Z, H, M, D, sx_z, sx_h, sx_m, sx_k,
                      dtype, reinterpret_cast<cudaStream_t>(stream));
+}
+
+QFA_API int qfa_quant_batch_per_token(const QfaQuantJob* jobs, int n_jobs, int dtype, qfa_stream_t stream) {
+  return quant_batch_entry(jobs, n_jobs, dtype, reinterpret_cast<cudaStream_t>(stream));
 }
 
 QFA_API int qfa_dequant_per_token(const int8_t* codes, const uint16_t* scale_f16, const int8_t* zp, void* out, int64_t Z,
@@ -156,6 +162,10 @@ QFA_API int qfa_attn_bwd(const QfaBwdArgs* a, qfa_stream_t stream) {
 
 QFA_API int qfa_selftest_wait_timeout(uint64_t budget_ns, int32_t* status, qfa_stream_t stream) {
   return wait_timeout_selftest_entry(budget_ns, status, reinterpret_cast<cudaStream_t>(stream));
+}
+
+QFA_API int qfa_probe_mma_rate(int form, int n, int iters, double* ops_out, int32_t* status, qfa_stream_t stream) {
+  return mma_probe_entry(form, n, iters, ops_out, status, reinterpret_cast<cudaStream_t>(stream));
 }
 
 QFA_API const char* qfa_strerror(int code) {

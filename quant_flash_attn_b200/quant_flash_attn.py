@@ -20,7 +20,7 @@ import os
 import torch
 
 from . import _lib
-from .asymmetric_quant import _DT, _require_cuda, _stream, _quantize
+from .asymmetric_quant import _DT, _require_cuda, _stream, _quantize, _quantize_batch
 
 
 def _next_power_of_2(n: int) -> int:
@@ -156,6 +156,8 @@ def quantize_qkv(q, k, v):
 
     Returns three tuples (codes, scale, zp, rowsum, dequantized-or-None); only V carries the
     dequantized 16-bit tensor (the P.V operand, quant_flash_attn.py:65-66)."""
+    if q.dtype == k.dtype == v.dtype and q.device == k.device == v.device:
+        return tuple(_quantize_batch((q, k, v), (False, False, True)))        # one launch for the three tensors
     return _quantize(q, True, False), _quantize(k, True, False), _quantize(v, True, True)
 
 

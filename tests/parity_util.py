@@ -31,9 +31,9 @@ def gen(shape, dtype, seed, kind="normal"):
     return x.to(dtype)
 
 
-def measure(got, want, p_rounding=0.0):
+def measure(got, want):
     """(scale of `want`, max-abs error, max-abs error beyond the storage rounding of got's dtype, cosine)."""
-    storage = HALF_ULP.get(got.dtype, 0.0) + p_rounding
+    storage = HALF_ULP.get(got.dtype, 0.0)
     got, want = got.detach().float().cpu().flatten(), want.detach().float().cpu().flatten()
     scale = want.abs().max().item()
     diff = (got - want).abs()
@@ -43,18 +43,22 @@ def measure(got, want, p_rounding=0.0):
 
 
 def close(got, want, rel=REL_TOL, cos=COS_TOL, what="", p_rounding=0.0):
-    """`p_rounding`: a second per-element storage term, for forward outputs of rows whose softmax sits on a
-    handful of keys.  The kernels (like the reference, quant_flash_attn.py:75) round the weights P to the 16-bit
-    dtype before P.V; where one weight carries the row, its rounding error (up to half an ulp) reaches the
-    output element undiminished instead of averaging out.  Only the tests that build such rows pass it."""
+    """`p_rounding` (half an ulp of the 16-bit dtype, or 0) is added to `rel` for results whose rows hang on ONE
+    rounded weight.  The kernels, like the reference (quant_flash_attn.py:75,156,159-160), round P and dS to the
+    16-bit dtype before the second products.  Where the softmax of a row sits on one or two keys, that single
+    rounding (or one that falls the other way because two evaluations differ in the last fp32 bit) reaches the
+    output undiminished instead of averaging out over many keys, and with two dominant keys of opposite dS the
+    affected output element can be far smaller than the term that moved: the error is bounded by half an ulp of
+    the OUTPUT SCALE, not of the element.  Only the tests that build such rows (logits growing along the key
+    axis; channels scaled x20) pass it; everything else is held to the plain bound."""
     assert torch.isfinite(got).all(), what
-    scale, raw, excess, c = measure(got, want, p_rounding)
-    beyond_output_storage = excess if not p_rounding else measure(got, want)[2]
+    scale, raw, excess, c = measure(got, want)
     REPORT.append({"what": what, "dtype": str(got.dtype).replace("torch.", ""), "scale": scale,
                    "max_abs_over_scale": raw / max(scale, 1e-30),
-                   "beyond_storage_over_scale": max(beyond_output_storage, 0.0) / max(scale, 1e-30), "cosine": c,
-                   "second_storage_term": bool(p_rounding)})
-    assert excess <= rel * scale + 1e-5, f"{what}: max-abs excess {excess:.3e} > {rel} * {scale:.3e}"
+                   "beyond_storage_over_scale": max(excess, 0.0) / max(scale, 1e-30), "cosine": c,
+                   "bound": rel + p_rounding})
+    assert excess <= (rel + p_rounding) * scale + 1e-5, \
+        f"{what}: max-abs excess {excess:.3e} > {rel + p_rounding} * {scale:.3e}"
     if scale > 1e-4:
         assert c >= cos, f"{what}: cosine {c}"
 

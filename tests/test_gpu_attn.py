@@ -173,7 +173,7 @@ def test_int8_mode_growing_logits(qfa, dtype, causal, slope):
     assert torch.isfinite(lse).all()
     assert ((lse.cpu() - lse_ref).abs() <= 2e-3 + 1e-5 * lse_ref.abs()).all()
     # the rows built here sit on their last few keys: the one case (with outlier channels at the headline size) that
-    # gets the second storage term of parity_util.close
+    # gets the extra half ulp of parity_util.close
     _close(o, o_ref, what=f"int8 growing-logits slope {slope} causal={causal} {dtype} o".replace("torch.", ""),
            p_rounding=HALF_ULP[dtype])
 

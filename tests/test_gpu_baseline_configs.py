@@ -15,7 +15,7 @@ import pytest
 import torch
 
 import oracle
-from parity_util import HALF_ULP, close, gen, head_quant
+from parity_util import HALF_ULP, REL_TOL, close, gen, head_quant
 
 pytestmark = pytest.mark.gpu
 
@@ -79,21 +79,24 @@ def test_config2_headline_B4H32S4096D128(qfa, causal):
     """B4 H32 S4096 D128, bf16 N(0,1) with 1 % of the channels x20: forward AND backward, two whole heads
     against the oracle; all 128 heads of the tcgen05 kernels against the mma.sync kernels."""
     q, k, v, do = _per_head_inputs(4, 32, 4096, 128, "outlier", seed=7)
-    do = torch.randn_like(do)
+    do = torch.randn(do.shape, device="cuda", generator=torch.Generator(device="cuda").manual_seed(8)).to(do.dtype)
     tag = "C2 " + ("causal" if causal else "non-causal")
     # channels scaled x20 put the softmax of most rows on one or two keys, so a single 16-bit rounding of P or dS
-    # (or one that falls the other way because kernel and oracle differ in the last fp32 bit) reaches an output
-    # element undiminished: outputs and gradients of THIS configuration get the second storage term of
-    # parity_util.close; LSE keeps its plain bound, and every other configuration the plain 2e-3
+    # (or one that falls the other way because kernel and oracle differ in the last fp32 bit) reaches the output
+    # undiminished: outputs and gradients of THIS configuration get the extra half ulp of parity_util.close;
+    # LSE keeps its plain bound, and every other configuration the plain 2e-3
     qq, kq, vq, o, lse, grads = _check_heads(qfa, tag, q, k, v, do, causal, heads=((0, 0), (3, 17)),
                                              p_rounding=HALF_ULP[torch.bfloat16])
     sm = 1.0 / math.sqrt(128)
     o_mma, lse_mma = qfa.int8_attention_forward(qq, kq, vq[:4], causal, sm, torch.bfloat16)
     assert (lse - lse_mma).abs().max().item() <= 2e-3
-    close(o, o_mma.float(), what=tag + " o tcgen05 vs mma.sync (128 heads)", p_rounding=HALF_ULP[torch.bfloat16])
+    # two implementations that are each within the bound of the oracle may differ by twice the bound
+    close(o, o_mma.float(), rel=2 * REL_TOL, what=tag + " o tcgen05 vs mma.sync (128 heads)",
+          p_rounding=HALF_ULP[torch.bfloat16])
     grads_mma = qfa.int8_attention_backward(qq, kq, vq, causal, sm, o, lse, do, use_tc=False)
     for name, a, b_ in zip(("dq", "dk", "dv"), grads, grads_mma):
-        close(a, b_.float(), what=f"{tag} {name} tcgen05 vs mma.sync (128 heads)", p_rounding=HALF_ULP[torch.bfloat16])
+        close(a, b_.float(), rel=2 * REL_TOL, what=f"{tag} {name} tcgen05 vs mma.sync (128 heads)",
+              p_rounding=HALF_ULP[torch.bfloat16])
 
 
 def test_config3_training_B8H16S2048D64_causal(qfa):

@@ -179,6 +179,39 @@ def test_quantizer_above_2_31_elements(qfa):
         del c, sc, xf, err
 
 
+def test_batched_quantizer_equals_separate_calls(qfa):
+    """qfa_quant_batch_per_token (Q, K, V in one launch; V also dequantized) against three separate calls: same bits.
+    Covers the one-launch path (same head dim, aligned), ragged token counts, a transposed view, and the fallback
+    (different head dims -> one launch per job)."""
+    from quant_flash_attn_b200 import _lib
+    from quant_flash_attn_b200.asymmetric_quant import _quantize, _quantize_batch
+    for dtype in (torch.bfloat16, torch.float16):
+        q = _inputs("outlier", (2, 3, 301, 128), dtype, 1).cuda()
+        k = _inputs("normal", (2, 3, 77, 128), dtype, 2).cuda()
+        v = _inputs("loguniform", (2, 77, 3, 128), dtype, 3).cuda().transpose(1, 2)      # (B,S,H,D) memory
+        n0 = _lib.launch_count()
+        got = _quantize_batch((q, k, v), (False, False, True))
+        assert _lib.launch_count() - n0 == 1
+        want = (_quantize(q, True, False), _quantize(k, True, False), _quantize(v, True, True))
+        for g, w in zip(got, want):
+            assert g[0].stride() == w[0].stride()
+            for a, b in zip(g, w):
+                assert (a is None and b is None) or torch.equal(a, b)
+        # different head dims: falls back to one launch per job, still the same bits
+        k64 = _inputs("normal", (2, 3, 77, 64), dtype, 4).cuda()
+        n0 = _lib.launch_count()
+        got = _quantize_batch((q, k64), (True, False))
+        assert _lib.launch_count() - n0 == 2
+        for g, w in zip(got, (_quantize(q, True, True), _quantize(k64, True, False))):
+            for a, b in zip(g, w):
+                assert (a is None and b is None) or torch.equal(a, b)
+    lib = _lib.load()
+    assert lib.qfa_quant_batch_per_token(None, 1, 1, None) == -1
+    jobs = (_lib.QfaQuantJob * 5)()
+    assert lib.qfa_quant_batch_per_token(jobs, 5, 1, None) == -3
+    assert lib.qfa_quant_batch_per_token(jobs, 1, 9, None) == -2
+
+
 def test_quantizer_rejects_bad_arguments(qfa):
     with pytest.raises(RuntimeError):
         qfa.asymmetric_quant_per_token(torch.zeros(1, 1, 2, 64, dtype=torch.float16))       # CPU tensor
