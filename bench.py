@@ -5,8 +5,9 @@
     python bench.py --profile-case quant|fwd|fwd_causal|bwd|shortq     (small fixed case for a profiler capture)
 
 Workload: INT8 attention forward at B=4 H=32 S=4096 D=128, bf16 inputs ~N(0,1) with 1 % of the channels scaled
-x20, seeded per (batch, head), non-causal.  One step = quantize Q, K, V per token (ONE launch of the batched
-quantizer; V is also written dequantized) + one int8 attention forward.  `value` = attention ops 4*B*H*D*S^2 of
+x20, seeded per (batch, head), non-causal.  One step = quantize Q, K, V per token (the batched quantizer, V also
+written dequantized) + the int8 attention forward, through the package's `quant_attention_forward`, which cuts
+the heads into four slices so that the quantizer of a slice overlaps the attention of the previous one.  `value` = attention ops 4*B*H*D*S^2 of
 the WHOLE workload per step / step time, in TOPS, inputs resident in HBM.
 
 With N > 1 the 128 (batch, head) units of that fixed workload are cut into N contiguous slices, one per rank
@@ -269,25 +270,26 @@ def measure_tensor_peaks(stream):
 
 
 class StepGraphs:
-    """The two launches of a step -- batched quantizer, attention forward -- each captured once into a CUDA graph
-    and replayed, so that a step costs two graph launches on the host instead of a dozen allocations and two ctypes
-    calls (at 16 heads per GPU a step is 0.2 ms of GPU time).  Falls back to eager calls if capture is refused."""
+    """One step -- quantize q, k, v and run the attention forward through the package's pipelined operator front
+    half (head slices on side streams: the quantizer of a slice overlaps the attention of the previous one) --
+    captured once into a CUDA graph and replayed, so that a step costs one graph launch on the host instead of
+    dozens of allocations and ctypes calls (at 16 heads per GPU a step is 0.2 ms of GPU time).  A second graph
+    holds the attention forward alone (one launch over all local heads) for the per-kernel timing.  Falls back
+    to eager calls if capture is refused."""
 
     def __init__(self, qfa, q, k, v, causal, sm, stream):
         self.qfa, self.q, self.k, self.v, self.causal, self.sm, self.stream = qfa, q, k, v, causal, sm, stream
-        self.o = torch.empty_like(q)
-        self.lse = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device)
         self.mode = "eager"
-        self.launches_per_step = None
         n0 = qfa.launch_count()
-        self._quant()
-        self._attn()
+        self._step()
         torch.cuda.synchronize()
         self.launches_per_step = qfa.launch_count() - n0
+        self._attn()
+        torch.cuda.synchronize()
         try:
-            self.g_quant, self.g_attn = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
-            with torch.cuda.graph(self.g_quant):
-                self._quant()
+            self.g_step, self.g_attn = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.g_step):
+                self._step()
             with torch.cuda.graph(self.g_attn):
                 self._attn()
             torch.cuda.synchronize()
@@ -296,25 +298,24 @@ class StepGraphs:
             self.capture_error = repr(e)[:200]
             torch.cuda.synchronize()
 
-    def _quant(self):
-        self.qq, self.kq, self.vq = self.qfa.quantize_qkv(self.q, self.k, self.v)
+    def _step(self):
+        self.o, self.lse, self.qq, self.kq, self.vq = self.qfa.quant_attention_forward(self.q, self.k, self.v,
+                                                                                      self.causal, self.sm)
 
     def _attn(self):
         self.qfa.int8_attention_forward(self.qq, self.kq, self.vq, self.causal, self.sm, self.q.dtype, o=self.o, lse=self.lse)
 
-    def step(self, record=None):
+    def step(self):
         if self.mode == "cuda-graph":
-            self.g_quant.replay()
+            self.g_step.replay()
         else:
-            self._quant()
-        if record is not None:
-            record[0].record(self.stream)
+            self._step()
+
+    def attn_only(self):
         if self.mode == "cuda-graph":
             self.g_attn.replay()
         else:
             self._attn()
-        if record is not None:
-            record[1].record(self.stream)
 
 
 class RotatingRunner:
@@ -330,8 +331,12 @@ class RotatingRunner:
         self.qq, self.kq, self.vq = r0.qq, r0.kq, r0.vq
         self.capture_error = getattr(r0, "capture_error", None)
 
-    def step(self, record=None):
-        self.runners[self.i % len(self.runners)].step(record)
+    def step(self):
+        self.runners[self.i % len(self.runners)].step()
+        self.i += 1
+
+    def attn_only(self):
+        self.runners[self.i % len(self.runners)].attn_only()
         self.i += 1
 
 
@@ -343,22 +348,20 @@ def rotation_count(bytes_per_step: float) -> int:
     return max(1, int(math.ceil(2 * L2_BYTES / max(bytes_per_step, 1.0))))
 
 
-def timed_steps(runner, steps, stream, barrier, per_step_events=True):
-    """`steps` steps bracketed by a barrier + synchronize on both sides; returns (total ms, mean ms of the attention
-    launch from per-step events, wall-clock window)."""
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+def timed_steps(runner, steps, stream, barrier, attn_only=False):
+    """`steps` steps (or launches of the attention forward alone) bracketed by a barrier + synchronize on both
+    sides, timed with CUDA events on the launching stream; returns (total ms, wall-clock window)."""
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    fn = runner.attn_only if attn_only else runner.step
     barrier()
     w0 = time.time()
     t0.record(stream)
-    for i in range(steps):
-        runner.step(ev[i] if per_step_events else None)
+    for _ in range(steps):
+        fn()
     t1.record(stream)
     barrier()
     w1 = time.time()
-    total = t0.elapsed_time(t1)
-    attn = sum(a.elapsed_time(b) for a, b in ev) / steps if per_step_events else None
-    return total, attn, (w0, w1)
+    return t0.elapsed_time(t1), (w0, w1)
 
 
 def single_gpu_extras(qfa, extra, runner, dev, stream, sm):
@@ -532,7 +535,12 @@ def run_ours(args):
         for _ in range(20):
             runner.step()
         torch.cuda.synchronize()
-    ms_total, attn_ms, (wall0, wall1) = timed_steps(runner, args.steps, stream, barrier)
+    ms_total, (wall0, wall1) = timed_steps(runner, args.steps, stream, barrier)
+    # the attention forward alone (one launch over the rank's heads, same rotating buffers), timed the same way
+    # right after the step loop: inside a step its launches overlap the next slice's quantizer, so its own
+    # duration cannot be read from events placed between them
+    attn_total, (_, wall1) = timed_steps(runner, args.steps, stream, barrier, attn_only=True)
+    attn_ms = attn_total / args.steps
     qfa.check_kernel_status()
     if rank == 0:
         sampler.window(wall0, wall1)
@@ -592,7 +600,7 @@ def run_ours(args):
         rep = StepGraphs(qfa, fq, fk, fv, False, sm, stream)        # 403 MB of inputs per step: larger than L2
         for _ in range(3):
             rep.step()
-        r_total, _, _ = timed_steps(rep, max(5, min(args.steps, 20)), stream, barrier, per_step_events=False)
+        r_total, _ = timed_steps(rep, max(5, min(args.steps, 20)), stream, barrier)
         (r_total,) = max_over_ranks(r_total)
         r_step = r_total / max(5, min(args.steps, 20))
         extra["weak_scaling_replicas"] = {"ms_per_step": r_step, "global_batch": B * world,
@@ -656,6 +664,7 @@ def result_line(args, world, value, ms_step, ms_total, attn_ms, ops_local, launc
         "traffic": n_local * (34.55e6 / 16) + n_local * S * D * 2,
         "traffic_note": "scaled from a 16-head capture: 2.16 MB read per head + output bytes",
         "ms_per_launch": attn_ms,
+        "timing": "CUDA events around `steps` launches of the forward alone, right after the step loop",
     }
     if "int8_ss_n128" in tp:
         # half of the forward's operations run as int8 MMAs (Q.K^T), half as bf16 MMAs (P.V): the time both need at

@@ -16,7 +16,7 @@ from .asymmetric_quant import (  # noqa: F401
 )
 from .quant_flash_attn import (  # noqa: F401
     QuantFlashAttention, quant_flash_attn, QuantAttention, quant_attention,
-    quantize_qkv, int8_attention_forward, int8_attention_backward, dequantize_16bit,
+    quantize_qkv, quant_attention_forward, int8_attention_forward, int8_attention_backward, dequantize_16bit,
     HostAttentionPipeline, quant_attention_host, check_kernel_status,
 )
 from .flash_attn_interface import (  # noqa: F401
@@ -28,7 +28,7 @@ from ._lib import launch_count  # noqa: F401
 __all__ = [
     "asymmetric_quant_per_token", "asymmetric_quant_per_token_ex", "dequantize_per_token",
     "QuantFlashAttention", "quant_flash_attn", "QuantAttention", "quant_attention",
-    "quantize_qkv", "int8_attention_forward", "int8_attention_backward", "dequantize_16bit",
+    "quantize_qkv", "quant_attention_forward", "int8_attention_forward", "int8_attention_backward", "dequantize_16bit",
     "HostAttentionPipeline", "quant_attention_host", "check_kernel_status",
     "quant_flash_attn_func", "quant_flash_attn_kvpacked_func", "quant_flash_attn_varlen_func",
     "all_gather_heads", "head_slice", "shard_bounds", "launch_count",

@@ -48,15 +48,16 @@ def _quantize(x: torch.Tensor, want_sum: bool, want_dequant: bool):
     return codes, scale, zp, rowsum, xhat
 
 
-def _quantize_batch(tensors, want_dequant):
+def _quantize_batch(tensors, want_dequant, outs=None):
     """Quantizes several (B,H,S,D) tensors of one dtype on one device with a single library call (one kernel launch
     when they share the head dimension and have 16-byte aligned rows).  `want_dequant[i]` asks for the dequantized
     copy of tensor i.  Returns one (codes, scale, zp, rowsum, dequantized-or-None) tuple per tensor, bit-identical
-    to separate `_quantize` calls."""
+    to separate `_quantize` calls.  `outs` (optional) supplies those tuples pre-allocated: codes with the strides
+    of its input, the others contiguous; nothing is allocated then."""
     import ctypes as C
     x0 = tensors[0]
     jobs = (_lib.QfaQuantJob * len(tensors))()
-    outs, keep = [], []
+    results, keep = [], []
     for i, (x, dq) in enumerate(zip(tensors, want_dequant)):
         if x.dim() != 4:
             raise ValueError("expected a 4-D tensor (Batch, Num_Heads, Seq_Len, Head_Dim)")
@@ -64,22 +65,27 @@ def _quantize_batch(tensors, want_dequant):
         if x.dtype != x0.dtype or x.dtype not in _DT or x.device != x0.device:
             raise TypeError("expected float16 or bfloat16 tensors of one dtype on one device")
         Z, H, M, K = x.shape
-        codes = torch.empty_like(x, dtype=torch.int8)        # the input's strides (asymmetric_quant.py:64,127)
-        if codes.stride() != x.stride():
-            x = x.contiguous()
-            codes = torch.empty_like(x, dtype=torch.int8)
-        scale = torch.empty(Z, H, M, 1, dtype=torch.float16, device=x.device)
-        zp = torch.empty(Z, H, M, 1, dtype=torch.int8, device=x.device)
-        rowsum = torch.empty(Z, H, M, dtype=torch.int32, device=x.device)
-        xhat = torch.empty(Z, H, M, K, dtype=x.dtype, device=x.device) if dq else None
+        if outs is not None:
+            codes, scale, zp, rowsum, xhat = outs[i]
+            if codes.stride() != x.stride() or (dq and xhat is None):
+                raise ValueError("pre-allocated quantizer outputs do not match the input")
+        else:
+            codes = torch.empty_like(x, dtype=torch.int8)    # the input's strides (asymmetric_quant.py:64,127)
+            if codes.stride() != x.stride():
+                x = x.contiguous()
+                codes = torch.empty_like(x, dtype=torch.int8)
+            scale = torch.empty(Z, H, M, 1, dtype=torch.float16, device=x.device)
+            zp = torch.empty(Z, H, M, 1, dtype=torch.int8, device=x.device)
+            rowsum = torch.empty(Z, H, M, dtype=torch.int32, device=x.device)
+            xhat = torch.empty(Z, H, M, K, dtype=x.dtype, device=x.device) if dq else None
         jobs[i] = _lib.QfaQuantJob(x.data_ptr(), codes.data_ptr(), scale.data_ptr(), zp.data_ptr(), rowsum.data_ptr(),
                                    xhat.data_ptr() if dq else None, Z, H, M, K, *x.stride())
         keep.append(x)
-        outs.append((codes, scale, zp, rowsum, xhat))
+        results.append((codes, scale, zp, rowsum, xhat))
     with torch.cuda.device(x0.device):
         rc = _lib.load().qfa_quant_batch_per_token(jobs, len(tensors), _DT[x0.dtype], _stream(x0))
     _lib.check(rc, "qfa_quant_batch_per_token")
-    return outs
+    return results
 
 
 def asymmetric_quant_per_token(input_tensor: torch.Tensor):

@@ -195,6 +195,75 @@ def int8_attention_forward(qq, kq, vq, causal: bool, sm_scale: float, dtype: tor
     return o, lse
 
 
+_side_streams = {}
+
+
+def _streams_for(device, n: int):
+    """`n` side streams of `device`, created once."""
+    key = torch.device(device).index
+    have = _side_streams.setdefault(key, [])
+    with torch.cuda.device(device):
+        while len(have) < n:
+            have.append(torch.cuda.Stream())
+    return have[:n]
+
+
+def quant_attention_forward(q, k, v, causal: bool, sm_scale: float, chunks: int = 4):
+    """Front half of the int8 operator: quantize q, k, v per token and run the forward.  Returns
+    (o, lse, qq, kq, vq) with qq, kq, vq as from `quantize_qkv`.
+
+    Heads are independent units of the path, so the flattened (batch x head) axis is cut into `chunks` slices that
+    run on side streams: the quantizer of slice c+1 (bound by HBM) overlaps the attention of slice c (bound by
+    the SMs), and the attention launches of all slices queue up behind each other like one launch.  What stays
+    exposed of the quantizer is its first slice.  Every output is allocated up front on the caller's stream, the
+    side streams only fill slices of it, and the caller's stream waits for them before this function returns.
+    Results are bit-identical to `quantize_qkv` followed by `int8_attention_forward`.  Operands that are not
+    contiguous (B,H,S,D) tensors of one dtype, or too few heads, take that plain two-call route."""
+    from .sharding import shard_bounds
+    B, H, Sq, D = q.shape
+    Skv = k.shape[2]
+    n = B * H
+    plain = (chunks <= 1 or n < 2 * chunks or k.shape[:2] != (B, H) or v.shape != k.shape
+             or not (q.is_contiguous() and k.is_contiguous() and v.is_contiguous())
+             or not (q.dtype == k.dtype == v.dtype) or not (q.device == k.device == v.device))
+    if plain:
+        qq, kq, vq = quantize_qkv(q, k, v)
+        o, lse = int8_attention_forward(qq, kq, vq, causal, sm_scale, q.dtype, o=torch.empty_like(q))
+        return o, lse, qq, kq, vq
+    _check_head_dim(D)
+    dev, dt = q.device, q.dtype
+
+    def alloc(S_, dequant):
+        return (torch.empty((B, H, S_, D), dtype=torch.int8, device=dev),
+                torch.empty((B, H, S_, 1), dtype=torch.float16, device=dev),
+                torch.empty((B, H, S_, 1), dtype=torch.int8, device=dev),
+                torch.empty((B, H, S_), dtype=torch.int32, device=dev),
+                torch.empty((B, H, S_, D), dtype=dt, device=dev) if dequant else None)
+
+    qq, kq, vq = alloc(Sq, False), alloc(Skv, False), alloc(Skv, True)
+    o = torch.empty_like(q)
+    lse = torch.empty((B, H, Sq), dtype=torch.float32, device=dev)
+    flat = lambda t: None if t is None else t.view(1, n, *t.shape[2:])
+    xf = [flat(t) for t in (q, k, v)]
+    qf, kf, vf = ([flat(t) for t in tup] for tup in (qq, kq, vq))
+    of, lf = flat(o), flat(lse)
+    main = torch.cuda.current_stream(dev)
+    fork = torch.cuda.Event()
+    fork.record(main)
+    for c, side in enumerate(_streams_for(dev, chunks)):
+        a, b = shard_bounds(n, chunks, c)
+        cut = lambda tup: tuple(None if t is None else t[:, a:b] for t in tup)
+        side.wait_event(fork)
+        with torch.cuda.stream(side):
+            outs = [cut(qf), cut(kf), cut(vf)]
+            _quantize_batch([t[:, a:b] for t in xf], (False, False, True), outs=outs)
+            int8_attention_forward(outs[0], outs[1], outs[2], causal, sm_scale, dt, o=of[:, a:b], lse=lf[:, a:b])
+            done = torch.cuda.Event()
+            done.record(side)
+        main.wait_event(done)
+    return o, lse, qq, kq, vq
+
+
 def dequantize_16bit(codes, scale, zp, dtype: torch.dtype) -> torch.Tensor:
     """(code - zp) * scale rounded to `dtype` as a contiguous (B,H,S,D) tensor (quant_flash_attn.py:65-66)."""
     B, H, S, D = codes.shape
@@ -269,10 +338,9 @@ class QuantAttention(torch.autograd.Function):
                 raise TypeError("q, k, v must share dtype float16 or bfloat16")
         if k.shape != v.shape or q.shape[:2] != k.shape[:2] or q.shape[3] != k.shape[3]:
             raise ValueError("expected q (B,H,Sq,D) and k, v (B,H,Skv,D)")
-        qq, kq, vq = quantize_qkv(q, k, v)
         # the output takes q's memory layout (the kernels write through strides), so a (B,S,H,D) caller that
         # passes transposed views gets its result in (B,S,H,D) memory without a copy
-        o, lse = int8_attention_forward(qq, kq, vq, causal, sm_scale, q.dtype, o=torch.empty_like(q))
+        o, lse, qq, kq, vq = quant_attention_forward(q, k, v, causal, sm_scale)
         ctx.save_for_backward(o, lse, *qq[:4], *kq[:4], *vq[:3], vq[4])
         ctx.causal, ctx.sm_scale = bool(causal), float(sm_scale)
         return o

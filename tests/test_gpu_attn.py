@@ -193,6 +193,30 @@ def test_host_pipeline_matches_device_operator(qfa, causal):
     assert torch.equal(got2, want)
 
 
+@pytest.mark.parametrize("causal", [False, True])
+def test_pipelined_front_half_equals_two_calls(qfa, causal):
+    """quant_attention_forward (heads cut into slices on side streams, quantizer of a slice overlapping the
+    attention of the previous one) returns the bits of quantize_qkv + int8_attention_forward: 11 heads over 4
+    slices is ragged; a (B,S,H,D) view and a 3-head problem take the plain route."""
+    B, H, S, D = 1, 11, 300, 128
+    q, k, v = (_gen((B, H, S, D), torch.bfloat16, s, "outlier").cuda() for s in (61, 62, 63))
+    sm = 1.0 / math.sqrt(D)
+    o, lse, qq, kq, vq = qfa.quant_attention_forward(q, k, v, causal, sm)
+    torch.cuda.synchronize()
+    qq2, kq2, vq2 = qfa.quantize_qkv(q, k, v)
+    o2, lse2 = qfa.int8_attention_forward(qq2, kq2, vq2, causal, sm, torch.bfloat16)
+    assert torch.equal(o, o2) and torch.equal(lse, lse2)
+    for a, b in zip(qq + kq + vq, qq2 + kq2 + vq2):
+        assert (a is None and b is None) or (a.shape == b.shape and torch.equal(a, b))
+    # twice in a row on the same side streams, then the autograd operator on top of it
+    o3 = qfa.quant_attention_forward(q, k, v, causal, sm)[0]
+    assert torch.equal(o3, o2)
+    assert torch.equal(qfa.quant_attention(q, k, v, causal, sm), o2)
+    qt = q.transpose(1, 2).contiguous().transpose(1, 2)            # (B,S,H,D) memory
+    assert torch.equal(qfa.quant_attention_forward(qt, k, v, causal, sm)[0], o2)
+    assert torch.equal(qfa.quant_attention_forward(q[:, :3], k[:, :3], v[:, :3], causal, sm)[0], o2[:, :3])
+
+
 def test_training_shape_properties(qfa):
     """BASELINE config 3 (B8 H16 S2048 D64 causal) at full size: the oracle is too slow there, so
     check size-independent properties: finite outputs, row 0 attends only to token 0, gradient
