@@ -277,6 +277,8 @@ class StepGraphs:
     holds the attention forward alone (one launch over all local heads) for the per-kernel timing.  Falls back
     to eager calls if capture is refused."""
 
+    eager_only = False      # --eager: no graph capture (for a profiler's launch list)
+
     def __init__(self, qfa, q, k, v, causal, sm, stream):
         self.qfa, self.q, self.k, self.v, self.causal, self.sm, self.stream = qfa, q, k, v, causal, sm, stream
         self.mode = "eager"
@@ -286,6 +288,8 @@ class StepGraphs:
         self.launches_per_step = qfa.launch_count() - n0
         self._attn()
         torch.cuda.synchronize()
+        if StepGraphs.eager_only:
+            return
         try:
             self.g_step, self.g_attn = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
             with torch.cuda.graph(self.g_step):
@@ -444,8 +448,37 @@ def single_gpu_extras(qfa, extra, runner, dev, stream, sm):
         a_, b2, c = (t.detach().requires_grad_() for t in (tq, tk, tv))
         qfa.quant_attention(a_, b2, c, True, tsm).backward(tdo)
     t_ms = time_ms(train_step, stream, reps=5)
-    extra["fwd_bwd_B8H16S2048D64_causal"] = {"ms": t_ms, "TOPS": 3.5 * fwd_ops(tb, th, ts, ts, td, True) / t_ms / 1e9}
-    del tq, tk, tv, tdo
+    c3 = {"ms": t_ms, "TOPS": 3.5 * fwd_ops(tb, th, ts, ts, td, True) / t_ms / 1e9,
+          "note": "autograd operator, eager: quantize + forward + backward, a dozen launches per step"}
+    # the same step captured in a CUDA graph (a step is well under a millisecond of GPU time, so the eager figure
+    # is bound by the host's launches and allocations, not by the kernels)
+    try:
+        a_, b2, c = (t.detach().clone().requires_grad_() for t in (tq, tk, tv))
+        side = torch.cuda.Stream()
+        side.wait_stream(stream)
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                qfa.quant_attention(a_, b2, c, True, tsm).backward(tdo)
+                a_.grad = b2.grad = c.grad = None
+        stream.wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            qfa.quant_attention(a_, b2, c, True, tsm).backward(tdo)
+        g_ms = time_ms(g.replay, stream, reps=10)
+        c3["graph_ms"] = g_ms
+        c3["graph_TOPS"] = 3.5 * fwd_ops(tb, th, ts, ts, td, True) / g_ms / 1e9
+        del g, a_, b2, c
+    except Exception as e:        # noqa: BLE001
+        c3["graph_error"] = repr(e)[:200]
+        torch.cuda.synchronize()
+    # and the two attention kernels on their own (no quantizer, no dequantization, no delta pre-pass in the forward)
+    qq, kq, vq = qfa.quantize_qkv(tq, tk, tv)
+    o_, lse_ = qfa.int8_attention_forward(qq, kq, vq, True, tsm, torch.bfloat16)
+    c3["fwd_kernel_ms"] = time_ms(lambda: qfa.int8_attention_forward(qq, kq, vq, True, tsm, torch.bfloat16), stream, reps=10)
+    c3["bwd_ms"] = time_ms(lambda: qfa.int8_attention_backward(qq, kq, vq, True, tsm, o_, lse_, tdo), stream, reps=10)
+    extra["fwd_bwd_B8H16S2048D64_causal"] = c3
+    del tq, tk, tv, tdo, qq, kq, vq, o_, lse_
 
     # flash_attn_func-style front end: the headline workload handed over in (B,S,H,D) memory
     fq, fk, fv = (t.view(B, H, S, D).transpose(1, 2).contiguous() for t in (runner.q, runner.k, runner.v))
@@ -575,7 +608,8 @@ def run_ours(args):
             del o_, lse_
         return out
 
-    extra["B4H32S4096D128_partitioned"] = partition_extras()
+    if not args.skip_extras:
+        extra["B4H32S4096D128_partitioned"] = partition_extras()
 
     # ---- long context: B1 H32 S32768 D128 causal, log-uniform token magnitudes, its 32 heads partitioned
     def long_context():
@@ -592,10 +626,11 @@ def run_ours(args):
         heads = 32 * world if weak else 32
         return {"ms": ms, "TOPS": fwd_ops(1, heads, 32768, 32768, D, True) / ms / 1e9, "heads_total": heads}
 
-    extra["long_context_B1H32S32768D128_causal_fwd"] = long_context()
+    if not args.skip_extras:
+        extra["long_context_B1H32S32768D128_causal_fwd"] = long_context()
 
     # ---- with N > 1 also the other scaling mode: every rank runs the full per-GPU workload (replicas)
-    if world > 1 and not weak:
+    if world > 1 and not weak and not args.skip_extras:
         fq, fk, fv = make_heads(rank * n_units, (rank + 1) * n_units, S, D, dev, seed_base=1234)
         rep = StepGraphs(qfa, fq, fk, fv, False, sm, stream)        # 403 MB of inputs per step: larger than L2
         for _ in range(3):
@@ -607,7 +642,7 @@ def run_ours(args):
                                           "TOPS": fwd_ops(B * world, H, S, S, D) / r_step / 1e9}
         del rep, fq, fk, fv
 
-    if rank == 0 and world == 1:
+    if rank == 0 and world == 1 and not args.skip_extras:
         single_gpu_extras(qfa, extra, runner, dev, stream, sm)
 
     # ---- end to end through the public host-tensor operator: pinned host q, k, v in, pinned host o out, every
@@ -751,8 +786,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
                     help="with --gpus N > 1: partition the fixed workload (strong) or replicate it per GPU (weak)")
+    ap.add_argument("--skip-extras", action="store_true", help="only the timed step loop and the end-to-end leg")
+    ap.add_argument("--eager", action="store_true", help="launch every step eagerly instead of replaying CUDA graphs")
     ap.add_argument("--profile-case", default=None, choices=["quant", "fwd", "fwd_causal", "bwd", "shortq"])
     args = ap.parse_args()
+    StepGraphs.eager_only = args.eager
     if args.profile_case:
         run_profile_case(args.profile_case)
     elif args.impl == "reference":

@@ -70,6 +70,51 @@ def test_ref_mode_oracle_vs_reference(path):
     assert (delta - torch.from_numpy(g["delta"])).abs().max() <= 2e-3
 
 
+@pytest.mark.parametrize("path", ATTN_CASES, ids=[os.path.basename(p)[:-4] for p in ATTN_CASES])
+def test_ref_mode_oracle_with_kernel_semantics_vs_reference(path):
+    """round_p: P and dS rounded to the 16-bit dtype before the second products, as the reference's kernels do
+    (quant_flash_attn.py:75,156,159-160).  The fixtures come from those kernels, so this evaluation must sit at
+    least as close to them as the un-rounded one, and within 1e-3 of the output scale."""
+    g = np.load(path)
+    q, go = torch.from_numpy(g["q"]), torch.from_numpy(g["go"])
+    codes, scale, zp = (torch.from_numpy(g[k]) for k in ("codes", "scale", "zp"))
+    sm = float(g["sm_scale"])
+    o_ref, lse_ref = torch.from_numpy(g["o"]), torch.from_numpy(g["lse"])
+
+    def rel(a, b):
+        b = torch.from_numpy(b).float() if isinstance(b, np.ndarray) else b.float()
+        return ((a.float() - b).abs().max() / b.abs().max()).item()
+
+    o, lse = oracle.ref_mode_forward(q, codes, scale, zp, sm, round_output=False, round_p=True)
+    dq, dkv = oracle.ref_mode_backward(q, codes, scale, zp, sm, o_ref, lse_ref, go, round_output=False, round_p=True)
+    dq0, dkv0 = oracle.ref_mode_backward(q, codes, scale, zp, sm, o_ref, lse_ref, go, round_output=False)
+    assert rel(o, o_ref) <= 1e-3 and (lse - lse_ref).abs().max() <= 1e-3
+    assert rel(dq, g["dq"]) <= 1e-3 and rel(dkv, g["dkv"]) <= 1e-3
+    # the fixtures' own fp16 storage rounding (2^-11) is the floor both evaluations sit on
+    assert rel(dq, g["dq"]) <= rel(dq0, g["dq"]) + 2.0 ** -11 and rel(dkv, g["dkv"]) <= rel(dkv0, g["dkv"]) + 2.0 ** -11
+
+
+def test_int8_mode_round_p_and_row_chunks():
+    """int8 mode: row chunks do not change the result; round_p moves it by no more than the 16-bit rounding of the
+    weights; the backward's delta equals rowsum(o * do)."""
+    torch.manual_seed(3)
+    B, H, S, D = 1, 2, 160, 64
+    q, k, v, do = (torch.randn(B, H, S, D).bfloat16() for _ in range(4))
+    for causal in (False, True):
+        o, lse, quant = oracle.int8_mode_forward(q, k, v, causal, 0.125, round_output=False)
+        o_c, lse_c, _ = oracle.int8_mode_forward(q, k, v, causal, 0.125, round_output=False, quant=quant, row_chunk=48)
+        assert (o - o_c).abs().max() <= 1e-6 and (lse - lse_c).abs().max() <= 1e-6
+        o_r, _, _ = oracle.int8_mode_forward(q, k, v, causal, 0.125, round_output=False, quant=quant,
+                                             round_p=torch.bfloat16)
+        assert 0 < (o - o_r).abs().max() <= 2.0 ** -8 * v.float().abs().max()
+        g = oracle.int8_mode_backward(quant, causal, 0.125, o, lse, do, torch.bfloat16, round_output=False)
+        g_c = oracle.int8_mode_backward(quant, causal, 0.125, o, lse, do, torch.bfloat16, round_output=False,
+                                        row_chunk=48, return_delta=True)
+        for a, b in zip(g, g_c[:3]):
+            assert (a - b).abs().max() <= 1e-4 * a.abs().max()
+        assert (g_c[3] - (o.float() * do.float()).sum(-1)).abs().max() <= 1e-5
+
+
 def test_int8_identity_matches_dequantized_matmul():
     torch.manual_seed(0)
     q = torch.randn(1, 2, 64, 64).half()
