@@ -642,6 +642,28 @@ def run_ours(args):
                                           "TOPS": fwd_ops(B * world, H, S, S, D) / r_step / 1e9}
         del rep, fq, fk, fv
 
+    # ---- the same steps issued alternately on two streams: consecutive steps are independent (they use different
+    # copies of the inputs and their own outputs), so the head of step i+1 fills the SMs that the last, partial wave
+    # of step i leaves idle.  A throughput figure for a consumer that keeps two batches in flight; NOT the headline,
+    # whose steps run strictly one after the other.
+    if n_rot >= 2 and not args.skip_extras:
+        two = [torch.cuda.Stream(), torch.cuda.Stream()]
+        n2 = max(args.steps, 20)
+        barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record(stream)
+        for s_ in two:
+            s_.wait_stream(stream)
+        for i in range(n2):
+            with torch.cuda.stream(two[i & 1]):
+                runner.step()
+        for s_ in two:
+            stream.wait_stream(s_)
+        t1.record(stream)
+        barrier()
+        (t2,) = max_over_ranks(t0.elapsed_time(t1) / n2)
+        extra["steps_on_two_streams"] = {"ms_per_step": t2, "TOPS": ops_total / t2 / 1e9, "steps": n2}
+
     if rank == 0 and world == 1 and not args.skip_extras:
         single_gpu_extras(qfa, extra, runner, dev, stream, sm)
 

@@ -45,11 +45,14 @@ struct TcFwdParams {
   int32_t* status;
 };
 
-template <int D>
+// REF = the reference's arithmetic (quant_flash_attn.py:50-79): Q stays 16-bit (scaled by sm_scale and rounded
+// in shared memory), the one dequantized K/V tensor is both operands, logits come from a 16-bit MMA in fp32; no
+// int8 tiles, no per-column constants.
+template <int D, bool REF = false>
 struct TcCfg {
   static constexpr int BM = 128, BN = 128, NQT = 2;
-  static constexpr int KSTAGES = 2, VSTAGES = 2, MSTAGES = 4;
-  static constexpr int Q_BYTES = BM * D;                 // int8
+  static constexpr int KSTAGES = REF ? 0 : 2, VSTAGES = 2, MSTAGES = REF ? 0 : 4;
+  static constexpr int Q_BYTES = BM * D * (REF ? 2 : 1); // int8 codes, or 16-bit rows as D/64 panels of 128-byte rows
   static constexpr int K_BYTES = BN * D;                 // int8
   static constexpr int V_BYTES = BN * D * 2;             // 16-bit
   static constexpr int V_PANELS = D / 64;                // 64-element (128-byte) column panels
@@ -60,7 +63,7 @@ struct TcCfg {
   static constexpr int V_OFF = K_OFF + KSTAGES * K_BYTES;
   static constexpr int M_OFF = V_OFF + VSTAGES * V_BYTES;
   static constexpr int BAR_OFF = M_OFF + MSTAGES * M_BYTES;
-  static constexpr int NBARS = 1 + 2 * KSTAGES + 2 * VSTAGES + 2 * MSTAGES + 3 * NQT;
+  static constexpr int NBARS = 1 + 2 * KSTAGES + 2 * VSTAGES + 2 * MSTAGES + 3 * NQT + 1;   // + "Q scaled" (REF)
   static constexpr int MISC_OFF = BAR_OFF + NBARS * 8;
   static constexpr int SMEM = MISC_OFF + 16 + 1024;      // + slack for 1024-byte alignment of the base
   static constexpr int SOFTMAX_THREADS = 2 * NQT * BM;   // one warp per 16 rows; a thread owns 2 rows x 32 columns
@@ -85,6 +88,33 @@ struct RowConst2 {
 // 16x256b fragment layout: element [4n + 2*row + e] is column 8n + 2q + e.  `meta` points at this thread's three
 // 16-byte words of the block: z_k, -sum(k), s_k of its four columns, loaded once and used for both rows.  lim[k] = first masked column of row k relative to
 // (block start + 2q).  pw receives P packed to 16 bit in the 16x128b store layout (word 2n + row).
+// REF counterpart of softmax_block: s holds fp32 logits q~.k^ (q~ = q * sm_scale rounded, quant_flash_attn.py:52,68);
+// P = exp2(s * log2e - ref).
+template <typename T, bool MASKED, bool MAX_ONLY>
+__device__ __forceinline__ void softmax_block_ref(const uint32_t (&s)[8], const int (&lim)[2], const RowConst2& rc,
+                                                  float (&emax)[2], float2 (&lsum2)[2], uint32_t* pw) {
+  using H16 = Half16<T>;
+  const float2 l2e = make_float2(kLog2e, kLog2e);
+#pragma unroll
+  for (int n = 0; n < 2; ++n) {
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      float2 v = make_float2(__uint_as_float(s[4 * n + 2 * k]), __uint_as_float(s[4 * n + 2 * k + 1]));
+      v = __ffma2_rn(v, l2e, rc.nref2[k]);
+      if (MASKED) {
+        if (8 * n >= lim[k]) v.x = -INFINITY;
+        if (8 * n + 1 >= lim[k]) v.y = -INFINITY;
+      }
+      asm("max.f32 %0, %0, %1, %2;" : "+f"(emax[k]) : "f"(v.x), "f"(v.y));
+      if (!MAX_ONLY) {
+        const float p0 = fast_exp2(v.x), p1 = fast_exp2(v.y);
+        lsum2[k] = __fadd2_rn(lsum2[k], make_float2(p0, p1));
+        pw[2 * n + k] = H16::pack(p0, p1);            // P rounded to 16 bit (quant_flash_attn.py:75)
+      }
+    }
+  }
+}
+
 template <typename T, int BN, bool MASKED, bool MAX_ONLY>
 __device__ __forceinline__ void softmax_block(const uint32_t (&s)[8], const float4* meta, const int (&lim)[2],
                                               const RowConst2& rc, float (&emax)[2], float2 (&lsum2)[2],
@@ -124,11 +154,11 @@ __device__ __forceinline__ void softmax_block(const uint32_t (&s)[8], const floa
   }
 }
 
-template <typename T, int D>
-__global__ void __launch_bounds__(TcCfg<D>::THREADS, 1)
+template <typename T, int D, bool REF>
+__global__ void __launch_bounds__(TcCfg<D, REF>::THREADS, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const TcFwdParams p) {
-  using C = TcCfg<D>;
+  using C = TcCfg<D, REF>;
   using H16 = Half16<T>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -141,6 +171,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   constexpr int B_VFULL = B_KEMPTY + C::KSTAGES, B_VEMPTY = B_VFULL + C::VSTAGES;
   constexpr int B_MFULL = B_VEMPTY + C::VSTAGES, B_MEMPTY = B_MFULL + C::MSTAGES;
   constexpr int B_SFULL = B_MEMPTY + C::MSTAGES, B_PFULL = B_SFULL + C::NQT, B_ODONE = B_PFULL + C::NQT;
+  constexpr int B_QSCALED = B_ODONE + C::NQT;       // REF: the softmax warps have scaled Q in shared memory
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::MISC_OFF);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::MISC_OFF + 4);
 
@@ -174,6 +205,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       mbar_init(BAR(B_PFULL + t), C::SOFTMAX_THREADS / 64);   // one arrival per softmax warp of the tile
       mbar_init(BAR(B_ODONE + t), 1);
     }
+    mbar_init(BAR(B_QSCALED), C::SOFTMAX_THREADS / 32);
     fence_barrier_init();
   }
   if (warp == 2) {
@@ -201,48 +233,60 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       int q_tiles = 0;
       for (int t = 0; t < C::NQT; ++t) q_tiles += (n_t[t] > 0);
       mbar_arrive_expect_tx(BAR(B_QFULL), q_tiles * C::Q_BYTES);
-      for (int t = 0; t < C::NQT; ++t)
-        if (n_t[t] > 0) tma_load_4d(sbase + C::Q_OFF + t * C::Q_BYTES, &tmQ, BAR(B_QFULL), 0, m0 + t * C::BM, h, b);
+      for (int t = 0; t < C::NQT; ++t) {
+        if (n_t[t] == 0) continue;
+        if constexpr (REF) {      // 16-bit rows: D/64 panels of 128-byte rows, like the V^ tiles
+          for (int pn = 0; pn < C::V_PANELS; ++pn)
+            tma_load_4d(sbase + C::Q_OFF + t * C::Q_BYTES + pn * C::V_PANEL_BYTES, &tmQ, BAR(B_QFULL), pn * 64,
+                        m0 + t * C::BM, h, b);
+        } else {
+          tma_load_4d(sbase + C::Q_OFF + t * C::Q_BYTES, &tmQ, BAR(B_QFULL), 0, m0 + t * C::BM, h, b);
+        }
+      }
     }
     const int hkv = h / (p.H / p.Hkv);            // the K/V head this query head reads
     const int64_t tok_k0 = (static_cast<int64_t>(b) * p.Hkv + hkv) * p.Skv;
     bool ok = true;
     for (int j = 0; j < n_max && ok; ++j) {
       const int n0 = j * C::BN;
-      const int ks = j % C::KSTAGES, vs = j % C::VSTAGES, ms = j % C::MSTAGES;
-      // K tile
-      ok = mbar_wait(BAR(B_KEMPTY + ks), ((j / C::KSTAGES) & 1) ^ 1, abort_flag, p.epoch);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      if (lane == 0) {
-        mbar_arrive_expect_tx(BAR(B_KFULL + ks), C::K_BYTES);
-        tma_load_4d(sbase + C::K_OFF + ks * C::K_BYTES, &tmK, BAR(B_KFULL + ks), 0, n0, hkv, b);
-      }
-      // per-column constants z_k, -sum(k), s_k
-      ok = mbar_wait(BAR(B_MEMPTY + ms), ((j / C::MSTAGES) & 1) ^ 1, abort_flag, p.epoch);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      float* meta = reinterpret_cast<float*>(smem + C::M_OFF + ms * C::M_BYTES);
-#pragma unroll
-      for (int i = 0; i < C::BN / 32; ++i) {
-        const int col = i * 32 + lane;
-        const int n = n0 + col;
-        float sk = 0.f, zk = 0.f, nks = 0.f;
-        if (n < p.Skv) {
-          sk = half_bits_to_f32(p.k_scale[tok_k0 + n]);
-          zk = static_cast<float>(p.k_zp[tok_k0 + n]);
-          nks = -static_cast<float>(p.k_sum[tok_k0 + n]);
+      const int vs = j % C::VSTAGES;
+      if constexpr (!REF) {
+        const int ks = j % C::KSTAGES, ms = j % C::MSTAGES;
+        // K tile
+        ok = mbar_wait(BAR(B_KEMPTY + ks), ((j / C::KSTAGES) & 1) ^ 1, abort_flag, p.epoch);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (lane == 0) {
+          mbar_arrive_expect_tx(BAR(B_KFULL + ks), C::K_BYTES);
+          tma_load_4d(sbase + C::K_OFF + ks * C::K_BYTES, &tmK, BAR(B_KFULL + ks), 0, n0, hkv, b);
         }
-        // layout for the softmax threads: thread q of a quad owns columns 8n+2q, 8n+2q+1; the constants of two
-        // column groups (n even, n odd) are packed into three 16-byte words {z_k}, {-sum(k)}, {s_k}
-        const int n8 = col >> 3, qq = (col >> 1) & 3, e = col & 1;
-        float* dst = meta + (((n8 >> 1) * 4 + qq) * 3) * 4 + (n8 & 1) * 2 + e;
-        dst[0] = zk;
-        dst[4] = nks;
-        dst[8] = sk;
+        // per-column constants z_k, -sum(k), s_k
+        ok = mbar_wait(BAR(B_MEMPTY + ms), ((j / C::MSTAGES) & 1) ^ 1, abort_flag, p.epoch);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        float* meta = reinterpret_cast<float*>(smem + C::M_OFF + ms * C::M_BYTES);
+  #pragma unroll
+        for (int i = 0; i < C::BN / 32; ++i) {
+          const int col = i * 32 + lane;
+          const int n = n0 + col;
+          float sk = 0.f, zk = 0.f, nks = 0.f;
+          if (n < p.Skv) {
+            sk = half_bits_to_f32(p.k_scale[tok_k0 + n]);
+            zk = static_cast<float>(p.k_zp[tok_k0 + n]);
+            nks = -static_cast<float>(p.k_sum[tok_k0 + n]);
+          }
+          // layout for the softmax threads: thread q of a quad owns columns 8n+2q, 8n+2q+1; the constants of two
+          // column groups (n even, n odd) are packed into three 16-byte words {z_k}, {-sum(k)}, {s_k}
+          const int n8 = col >> 3, qq = (col >> 1) & 3, e = col & 1;
+          float* dst = meta + (((n8 >> 1) * 4 + qq) * 3) * 4 + (n8 & 1) * 2 + e;
+          dst[0] = zk;
+          dst[4] = nks;
+          dst[8] = sk;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(BAR(B_MFULL + ms));
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(BAR(B_MFULL + ms));
+      if (!ok) break;
       // V tile (D/64 panels of 128 bytes x BN rows)
       ok = mbar_wait(BAR(B_VEMPTY + vs), ((j / C::VSTAGES) & 1) ^ 1, abort_flag, p.epoch);
       ok = __all_sync(0xffffffffu, ok);
@@ -257,20 +301,34 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   } else if (warp == 1) {
     // ================================================================ MMA issuer (one thread)
     if (lane == 0) {
-      constexpr uint32_t kIdescQK = make_idesc(2, 1, 1, 0, 0, C::BM, C::BN);
       constexpr uint32_t kF16Fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+      // logits: int8 x int8 -> int32, or (REF) 16-bit x 16-bit -> fp32 with both operands K-major
+      constexpr uint32_t kIdescQK = REF ? make_idesc(1, kF16Fmt, kF16Fmt, 0, 0, C::BM, C::BN) : make_idesc(2, 1, 1, 0, 0, C::BM, C::BN);
       constexpr uint32_t kIdescPV = make_idesc(1, kF16Fmt, kF16Fmt, 0, 1, C::BM, D);
       constexpr uint64_t kQKSwz = (D == 128) ? kSwizzle128B : kSwizzle64B;
       bool ok = mbar_wait(BAR(B_QFULL), 0, abort_flag, p.epoch);
+      if (REF && ok) ok = mbar_wait(BAR(B_QSCALED), 0, abort_flag, p.epoch);   // Q * sm_scale, rounded, in place
       tc_fence_after_sync();
 
       auto issue_qk = [&](int j, int t) {
-        const int ks = j % C::KSTAGES;
-        const uint64_t da = make_smem_desc(sbase + C::Q_OFF + t * C::Q_BYTES, 16, C::QK_SWIZZLE_ROWS_BYTES, kQKSwz);
-        const uint64_t db = make_smem_desc(sbase + C::K_OFF + ks * C::K_BYTES, 16, C::QK_SWIZZLE_ROWS_BYTES, kQKSwz);
+        if constexpr (REF) {
+          // K^ is the V^ tile of stage j (the same tensor): rows = keys, 128-byte swizzled panels of 64 columns
+          const uint32_t kv = sbase + C::V_OFF + (j % C::VSTAGES) * C::V_BYTES;
 #pragma unroll
-        for (int k = 0; k < D / 32; ++k)
-          mma_i8_ss(tmem + C::S_COL + t * C::BN, desc_advance(da, k * 32), desc_advance(db, k * 32), kIdescQK, k > 0);
+          for (int k = 0; k < D / 16; ++k) {
+            const uint32_t off = (k / 4) * C::V_PANEL_BYTES + (k % 4) * 32;
+            const uint64_t da = make_smem_desc(sbase + C::Q_OFF + t * C::Q_BYTES + off, 16, 1024, kSwizzle128B);
+            const uint64_t db = make_smem_desc(kv + off, 16, 1024, kSwizzle128B);
+            mma_f16_ss(tmem + C::S_COL + t * C::BN, da, db, kIdescQK, k > 0);
+          }
+        } else {
+          const int ks = j % C::KSTAGES;
+          const uint64_t da = make_smem_desc(sbase + C::Q_OFF + t * C::Q_BYTES, 16, C::QK_SWIZZLE_ROWS_BYTES, kQKSwz);
+          const uint64_t db = make_smem_desc(sbase + C::K_OFF + ks * C::K_BYTES, 16, C::QK_SWIZZLE_ROWS_BYTES, kQKSwz);
+#pragma unroll
+          for (int k = 0; k < D / 32; ++k)
+            mma_i8_ss(tmem + C::S_COL + t * C::BN, desc_advance(da, k * 32), desc_advance(db, k * 32), kIdescQK, k > 0);
+        }
         mma_commit(BAR(B_SFULL + t));
       };
       auto issue_pv = [&](int j, int t) {
@@ -282,21 +340,28 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                      (j > 0 || k > 0) ? 1u : 0u);
         mma_commit(BAR(B_ODONE + t));
       };
+      // the tile the logits of step j need: the K stage (int8 mode) or the V^ stage itself (REF)
+      auto wait_k = [&](int j) {
+        if constexpr (REF) return mbar_wait(BAR(B_VFULL + j % C::VSTAGES), (j / C::VSTAGES) & 1, abort_flag, p.epoch);
+        else return mbar_wait(BAR(B_KFULL + j % C::KSTAGES), (j / C::KSTAGES) & 1, abort_flag, p.epoch);
+      };
+      auto release_k = [&](int j) {
+        if constexpr (!REF) mma_commit(BAR(B_KEMPTY + j % C::KSTAGES));
+      };
 
       if (ok && n_max > 0) {
-        ok = mbar_wait(BAR(B_KFULL + 0), 0, abort_flag, p.epoch);
+        ok = wait_k(0);
         if (ok) {
           tc_fence_after_sync();
           for (int t = 0; t < C::NQT; ++t)
             if (0 < n_t[t]) issue_qk(0, t);
-          mma_commit(BAR(B_KEMPTY + 0));
+          release_k(0);
         }
       }
       for (int j = 0; j < n_max && ok; ++j) {
         const int vs = j % C::VSTAGES;
         ok = mbar_wait(BAR(B_VFULL + vs), (j / C::VSTAGES) & 1, abort_flag, p.epoch);
         if (!ok) break;
-        const int ks1 = (j + 1) % C::KSTAGES;
         bool kwaited = false;
         for (int t = 0; t < C::NQT && ok; ++t) {
           if (j < n_t[t]) {
@@ -307,7 +372,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           }
           if (j + 1 < n_t[t]) {
             if (!kwaited) {
-              ok = mbar_wait(BAR(B_KFULL + ks1), ((j + 1) / C::KSTAGES) & 1, abort_flag, p.epoch);
+              ok = wait_k(j + 1);
               if (!ok) break;
               tc_fence_after_sync();
               kwaited = true;
@@ -317,7 +382,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
         if (!ok) break;
         mma_commit(BAR(B_VEMPTY + vs));
-        if (kwaited) mma_commit(BAR(B_KEMPTY + ks1));
+        if (kwaited) release_k(j + 1);
       }
     }
   }
@@ -344,7 +409,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     for (int k = 0; k < 2; ++k) {
       rowk[k] = m0 + t * C::BM + wq * 32 + hh * 16 + g + 8 * k;
       float A = 0.f, zq = 0.f, a = 0.f;
-      if (rowk[k] < p.Sq) {
+      if (!REF && rowk[k] < p.Sq) {
         const int64_t tk = static_cast<int64_t>(bh) * p.Sq + rowk[k];
         const int z = p.q_zp[tk];
         zq = static_cast<float>(z);
@@ -372,10 +437,32 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     float ref[2] = {0.f, 0.f}, l_run[2] = {0.f, 0.f};
     const int my_n = n_t[t];
     bool ok = true;
+    if constexpr (REF) {
+      // q~ = (q * sm_scale) rounded to T (quant_flash_attn.py:52), in place in shared memory: an element-wise
+      // pass does not care about the swizzled placement of the 16-byte chunks.  All sixteen warps share it.
+      ok = mbar_wait(BAR(B_QFULL), 0, abort_flag, p.epoch);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
+        uint4* qs = reinterpret_cast<uint4*>(smem + C::Q_OFF);
+        for (int c = tid - 128; c < C::NQT * C::Q_BYTES / 16; c += C::SOFTMAX_THREADS) {
+          uint4 v = qs[c];
+          float2 f;
+          f = H16::unpack(v.x); v.x = H16::pack(f.x * p.sm_scale, f.y * p.sm_scale);
+          f = H16::unpack(v.y); v.y = H16::pack(f.x * p.sm_scale, f.y * p.sm_scale);
+          f = H16::unpack(v.z); v.z = H16::pack(f.x * p.sm_scale, f.y * p.sm_scale);
+          f = H16::unpack(v.w); v.w = H16::pack(f.x * p.sm_scale, f.y * p.sm_scale);
+          qs[c] = v;
+        }
+        // generic-proxy writes must be visible to the tensor core's (async proxy) operand reads
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(BAR(B_QSCALED));
+      }
+    }
     for (int j = 0; j < n_max && ok; ++j) {
-      const int ms = j % C::MSTAGES;
+      const int ms = REF ? 0 : j % (REF ? 1 : C::MSTAGES);
       if (j < my_n) {
-        ok = mbar_wait(BAR(B_MFULL + ms), (j / C::MSTAGES) & 1, abort_flag, p.epoch);
+        if (!REF) ok = mbar_wait(BAR(B_MFULL + ms), (j / (REF ? 1 : C::MSTAGES)) & 1, abort_flag, p.epoch);
         if (ok) ok = mbar_wait(BAR(B_SFULL + t), j & 1, abort_flag, p.epoch);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -413,8 +500,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             int lim_b[2];
 #pragma unroll
             for (int k = 0; k < 2; ++k) lim_b[k] = lim[k] - blk * 16;
-            softmax_block<T, C::BN, MASKED, MAXONLY>(sreg[blk & 1], meta + blk * 12, lim_b, rc, emax, lsum2,
-                                                     pw + blk * 4);
+            if constexpr (REF)
+              softmax_block_ref<T, MASKED, MAXONLY>(sreg[blk & 1], lim_b, rc, emax, lsum2, pw + blk * 4);
+            else
+              softmax_block<T, C::BN, MASKED, MAXONLY>(sreg[blk & 1], meta + blk * 12, lim_b, rc, emax, lsum2,
+                                                       pw + blk * 4);
           }
         };
         auto quad_max = [&]() {
@@ -503,7 +593,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
         // one arrival per warp (the warp's reads of the constants are ordered before it by __syncwarp)
         __syncwarp();
-        if (lane == 0) mbar_arrive(BAR(B_MEMPTY + ms));
+        if (!REF && lane == 0) mbar_arrive(BAR(B_MEMPTY + ms));
 #pragma unroll
         for (int k = 0; k < 2; ++k) l_run[k] += lsum2[k].x + lsum2[k].y;
         tmem_st_16x128b_x16(tS, pw);
@@ -513,10 +603,12 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (lane == 0) mbar_arrive(BAR(B_PFULL + t));
       } else {
         // this query tile is done (causal): keep the per-column ring moving for the other tile
-        ok = mbar_wait(BAR(B_MFULL + ms), (j / C::MSTAGES) & 1, abort_flag, p.epoch);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        if (lane == 0) mbar_arrive(BAR(B_MEMPTY + ms));
+        if constexpr (!REF) {
+          ok = mbar_wait(BAR(B_MFULL + ms), (j / C::MSTAGES) & 1, abort_flag, p.epoch);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          if (lane == 0) mbar_arrive(BAR(B_MEMPTY + ms));
+        }
       }
     }
     // ---------------- epilogue: O / l -> 16 bit, LSE = (ref + log2 l) ln 2
@@ -567,20 +659,28 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (tid == 0 && *abort_flag && p.status) *p.status = QFA_STATUS_WAIT_TIMEOUT;
 }
 
-template <typename T, int D>
+template <typename T, int D, bool REF>
 static int launch_tc(const QfaFwdArgs& a, cudaStream_t stream) {
-  using C = TcCfg<D>;
+  using C = TcCfg<D, REF>;
   CUtensorMap tmQ, tmK, tmV;
   const CUtensorMapSwizzle qk_swz = (D == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   const CUtensorMapDataType vdt =
       std::is_same<T, __nv_bfloat16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  bool ok = make_tmap_4d(&tmQ, a.qq.codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, D, a.Sq, a.H, a.B, a.qq.stride[2],
-                         a.qq.stride[1], a.qq.stride[0], D, C::BM, qk_swz);
   const int64_t Hkv = a.Hkv ? a.Hkv : a.H;
-  ok = ok && make_tmap_4d(&tmK, a.k.codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, D, a.Skv, Hkv, a.B, a.k.stride[2],
-                          a.k.stride[1], a.k.stride[0], D, C::BN, qk_swz);
+  bool ok;
+  if (REF) {
+    // 16-bit Q with the caller's strides, in 64-column panels; the K tensor map is not used (K^ is the V^ tile)
+    ok = make_tmap_4d(&tmQ, a.q, vdt, 2, D, a.Sq, a.H, a.B, 2ull * a.q_stride[2], 2ull * a.q_stride[1],
+                      2ull * a.q_stride[0], 64, C::BM, CU_TENSOR_MAP_SWIZZLE_128B);
+  } else {
+    ok = make_tmap_4d(&tmQ, a.qq.codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, D, a.Sq, a.H, a.B, a.qq.stride[2],
+                      a.qq.stride[1], a.qq.stride[0], D, C::BM, qk_swz);
+    ok = ok && make_tmap_4d(&tmK, a.k.codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, D, a.Skv, Hkv, a.B, a.k.stride[2],
+                            a.k.stride[1], a.k.stride[0], D, C::BN, qk_swz);
+  }
   ok = ok && make_tmap_4d(&tmV, a.v_hat, vdt, 2, D, a.Skv, Hkv, a.B, 2ull * D, 2ull * D * a.Skv,
                           2ull * D * a.Skv * Hkv, 64, C::BN, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (REF) tmK = tmV;
   if (!ok) return cuda_fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
   TcFwdParams p;
   p.q_scale = a.qq.scale; p.q_zp = a.qq.zp; p.q_sum = a.qq.rowsum;
@@ -591,7 +691,7 @@ static int launch_tc(const QfaFwdArgs& a, cudaStream_t stream) {
   p.H = static_cast<int>(a.H); p.Hkv = static_cast<int>(Hkv); p.Sq = static_cast<int>(a.Sq); p.Skv = static_cast<int>(a.Skv);
   p.sm_scale = a.sm_scale; p.causal = a.causal; p.status = a.status;
   p.epoch = next_launch_epoch();
-  auto kern = attn_fwd_tc_kernel<T, D>;
+  auto kern = attn_fwd_tc_kernel<T, D, REF>;
   static DeviceOnce attr_done;
   int rc = once_per_device(attr_done, [&]() -> int {
     QFA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
@@ -638,22 +738,30 @@ int wait_timeout_selftest_entry(uint64_t budget_ns, int32_t* status, cudaStream_
   return QFA_OK;
 }
 
-// The tcgen05 kernel takes int8-mode problems with the dequantized V supplied by the quantizer.
+// The tcgen05 kernel takes int8-mode problems with the dequantized V supplied by the quantizer, and REF-mode
+// problems with more than 32 query rows whose one K/V tensor is supplied dequantized (v_hat): 16-bit Q and K^ = V^
+// feed a 16-bit MMA for the logits.  (Up to 32 query rows the short-query kernels, which read the int8 codes
+// directly, are the faster path.)
 int attn_fwd_tc_supported(const QfaFwdArgs& a) {
-  if (a.mode != QFA_MODE_INT8 || !a.v_hat) return 0;
+  if (!a.v_hat) return 0;
   if (a.D != 128 && a.D != 64) return 0;
-  if (!(a.sm_scale > 0.f)) return 0;
   if ((reinterpret_cast<uintptr_t>(a.v_hat) & 15) != 0) return 0;
+  if (a.mode == QFA_MODE_INT8) return a.sm_scale > 0.f ? 1 : 0;
+  if (a.mode != QFA_MODE_REF || a.causal || a.Sq <= 32 || !a.q) return 0;
+  if (a.k.codes != a.v.codes || a.k.scale != a.v.scale || a.k.zp != a.v.zp) return 0;
+  if (a.Hkv != 0 && a.Hkv != a.H) return 0;
   return 1;
 }
 
 int attn_fwd_tc_entry(const QfaFwdArgs& a, cudaStream_t stream) {
-  if (a.D == 128) {
-    return a.dtype == QFA_BF16 ? launch_tc<__nv_bfloat16, 128>(a, stream) : launch_tc<__half, 128>(a, stream);
+  const bool bf = a.dtype == QFA_BF16;
+  if (a.mode == QFA_MODE_REF) {
+    if (a.D == 128) return bf ? launch_tc<__nv_bfloat16, 128, true>(a, stream) : launch_tc<__half, 128, true>(a, stream);
+    if (a.D == 64) return bf ? launch_tc<__nv_bfloat16, 64, true>(a, stream) : launch_tc<__half, 64, true>(a, stream);
+    return QFA_ERR_HEAD_DIM;
   }
-  if (a.D == 64) {
-    return a.dtype == QFA_BF16 ? launch_tc<__nv_bfloat16, 64>(a, stream) : launch_tc<__half, 64>(a, stream);
-  }
+  if (a.D == 128) return bf ? launch_tc<__nv_bfloat16, 128, false>(a, stream) : launch_tc<__half, 128, false>(a, stream);
+  if (a.D == 64) return bf ? launch_tc<__nv_bfloat16, 64, false>(a, stream) : launch_tc<__half, 64, false>(a, stream);
   return QFA_ERR_HEAD_DIM;
 }
 
