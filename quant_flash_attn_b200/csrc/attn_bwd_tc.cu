@@ -48,14 +48,18 @@ struct TcBwdParams {
   int H, rows_total, cols_total;         // pass KV: rows = Skv, cols = Sq;  pass Q: rows = Sq, cols = Skv
   float sm_scale;
   int causal;
+  int fused;             // REF, pass KV: write dV + sm_scale * dK into out2 (quant_flash_attn.py:161)
   unsigned int epoch;
   int32_t* status;
 };
 
-template <int D>
+// REF = the reference's arithmetic (quant_flash_attn.py:133-166): 16-bit Q and the one dequantized K/V tensor
+// feed 16-bit MMAs for the logits; the "codes" tiles are 16-bit tiles then, the streamed stage holds two 16-bit
+// tiles [Y1 | Y2] (pass KV: Q and dO; pass Q: K^ = V^ alone), and there are no zero-point corrections.
+template <int D, bool REF = false>
 struct BwdTcCfg {
   static constexpr int BM = 128, BN = 128, STAGES = 2;
-  static constexpr int C_BYTES = 128 * D;              // int8 tile
+  static constexpr int C_BYTES = REF ? 128 * D * 2 : 128 * D;   // int8 tile, or (REF) a 16-bit tile in its place
   static constexpr int H_BYTES = 128 * D * 2;          // 16-bit tile
   static constexpr int PANELS = D / 64;
   static constexpr int PANEL_BYTES = 128 * 128;
@@ -63,7 +67,11 @@ struct BwdTcCfg {
   static constexpr int XC_OFF = 0;
   static constexpr int XH_OFF = XC_OFF + C_BYTES;
   static constexpr int ST_OFF = XH_OFF + H_BYTES;                      // stages: [Yc | Ya | Yb]
-  static constexpr int ST_BYTES = C_BYTES + 2 * H_BYTES;
+  static constexpr int ST_BYTES = REF ? 2 * H_BYTES : C_BYTES + 2 * H_BYTES;
+  // where the right operands of the four products live inside a stage
+  static constexpr int Y_T2B_KV = REF ? H_BYTES : C_BYTES, Y_T2B_Q = REF ? 0 : C_BYTES;     // T2: dO (KV) / V^ (Q)
+  static constexpr int Y_ACC1B = REF ? H_BYTES : C_BYTES;                                   // dV += P^T dO
+  static constexpr int Y_ACC2B = REF ? 0 : C_BYTES + H_BYTES;                               // dK += dS^T Q / dQ += dS K^
   static constexpr int M_OFF = ST_OFF + STAGES * ST_BYTES;
   static constexpr int BAR_OFF = M_OFF + STAGES * M_BYTES;
   static constexpr int KSTEPS = BN / 16;               // 16-column blocks = k-steps of the accumulating MMAs
@@ -133,17 +141,49 @@ __device__ __forceinline__ void bwd_block(const uint32_t (&s)[8], const uint32_t
   }
 }
 
+// REF counterpart: s holds fp32 q.k^ (un-scaled: the reference multiplies by sm_scale after the product,
+// quant_flash_attn.py:153); rc.a2 = sm_scale * log2e.  `meta` words 3, 4 carry -lse*log2e and -delta per column in
+// pass KV.
+template <typename T, bool KV_PASS, bool MASKED>
+__device__ __forceinline__ void bwd_block_ref(const uint32_t (&s)[8], const uint32_t (&d)[8], const float4* meta,
+                                              const int (&lo)[2], const int (&hi)[2], const BwdRow2& rc,
+                                              uint32_t (&pw)[4], uint32_t (&gw)[4]) {
+  using H16 = Half16<T>;
+  float4 l4 = make_float4(0.f, 0.f, 0.f, 0.f), d4 = l4;
+  if (KV_PASS) { l4 = meta[3]; d4 = meta[4]; }
+#pragma unroll
+  for (int n = 0; n < 2; ++n) {
+    const float2 l2 = n ? make_float2(l4.z, l4.w) : make_float2(l4.x, l4.y);
+    const float2 d2 = n ? make_float2(d4.z, d4.w) : make_float2(d4.x, d4.y);
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      float2 v = make_float2(__uint_as_float(s[4 * n + 2 * k]), __uint_as_float(s[4 * n + 2 * k + 1]));
+      v = __ffma2_rn(v, rc.a2[k], KV_PASS ? l2 : rc.nlse2[k]);
+      if (MASKED) {
+        if (8 * n < lo[k] || 8 * n >= hi[k]) v.x = -INFINITY;
+        if (8 * n + 1 < lo[k] || 8 * n + 1 >= hi[k]) v.y = -INFINITY;
+      }
+      const float p0 = fast_exp2(v.x), p1 = fast_exp2(v.y);
+      float2 dd = __fadd2_rn(make_float2(__uint_as_float(d[4 * n + 2 * k]), __uint_as_float(d[4 * n + 2 * k + 1])),
+                             KV_PASS ? d2 : rc.ndelta2[k]);
+      dd = __fmul2_rn(make_float2(p0, p1), dd);
+      pw[2 * n + k] = H16::pack(p0, p1);              // P rounded to 16 bit (quant_flash_attn.py:156)
+      gw[2 * n + k] = H16::pack(dd.x, dd.y);          // dS rounded to 16 bit (quant_flash_attn.py:159-160)
+    }
+  }
+}
+
 __device__ __forceinline__ void tmem_st_16x128b_x2(uint32_t taddr, const uint32_t (&r)[4]) {
   asm volatile("tcgen05.st.sync.aligned.16x128b.x2.b32 [%0], {%1, %2, %3, %4};"
                ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]) : "memory");
 }
 
-template <typename T, int D, bool KV_PASS>
-__global__ void __launch_bounds__(BwdTcCfg<D>::THREADS, 1)
+template <typename T, int D, bool KV_PASS, bool REF>
+__global__ void __launch_bounds__(BwdTcCfg<D, REF>::THREADS, 1)
 attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_constant__ CUtensorMap tmXh,
                    const __grid_constant__ CUtensorMap tmYc, const __grid_constant__ CUtensorMap tmYa,
                    const __grid_constant__ CUtensorMap tmYb, const TcBwdParams p) {
-  using C = BwdTcCfg<D>;
+  using C = BwdTcCfg<D, REF>;
   using H16 = Half16<T>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -213,7 +253,12 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
     if (lane == 0) {
       prefetch_tmap(&tmXc); prefetch_tmap(&tmXh); prefetch_tmap(&tmYc); prefetch_tmap(&tmYa); prefetch_tmap(&tmYb);
       mbar_arrive_expect_tx(BAR(B_XFULL), C::C_BYTES + C::H_BYTES);
-      tma_load_4d(sbase + C::XC_OFF, &tmXc, BAR(B_XFULL), 0, r0, h, b);
+      if constexpr (REF) {
+        for (int pn = 0; pn < C::PANELS; ++pn)
+          tma_load_4d(sbase + C::XC_OFF + pn * C::PANEL_BYTES, &tmXc, BAR(B_XFULL), pn * 64, r0, h, b);
+      } else {
+        tma_load_4d(sbase + C::XC_OFF, &tmXc, BAR(B_XFULL), 0, r0, h, b);
+      }
       for (int pn = 0; pn < C::PANELS; ++pn)
         tma_load_4d(sbase + C::XH_OFF + pn * C::PANEL_BYTES, &tmXh, BAR(B_XFULL), pn * 64, r0, h, b);
     }
@@ -226,11 +271,21 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
       if (!ok) break;
       const uint32_t stage = sbase + C::ST_OFF + st * C::ST_BYTES;
       if (lane == 0) {
-        mbar_arrive_expect_tx(BAR(B_YFULL + st), C::ST_BYTES);
-        tma_load_4d(stage, &tmYc, BAR(B_YFULL + st), 0, c0, h, b);
-        for (int pn = 0; pn < C::PANELS; ++pn) {
-          tma_load_4d(stage + C::C_BYTES + pn * C::PANEL_BYTES, &tmYa, BAR(B_YFULL + st), pn * 64, c0, h, b);
-          tma_load_4d(stage + C::C_BYTES + C::H_BYTES + pn * C::PANEL_BYTES, &tmYb, BAR(B_YFULL + st), pn * 64, c0, h, b);
+        if constexpr (REF) {
+          // [Y1 | Y2]: pass KV streams Q and dO, pass Q the one K^ = V^ tile
+          mbar_arrive_expect_tx(BAR(B_YFULL + st), KV_PASS ? 2 * C::H_BYTES : C::H_BYTES);
+          for (int pn = 0; pn < C::PANELS; ++pn) {
+            tma_load_4d(stage + pn * C::PANEL_BYTES, &tmYc, BAR(B_YFULL + st), pn * 64, c0, h, b);
+            if (KV_PASS)
+              tma_load_4d(stage + C::H_BYTES + pn * C::PANEL_BYTES, &tmYa, BAR(B_YFULL + st), pn * 64, c0, h, b);
+          }
+        } else {
+          mbar_arrive_expect_tx(BAR(B_YFULL + st), C::ST_BYTES);
+          tma_load_4d(stage, &tmYc, BAR(B_YFULL + st), 0, c0, h, b);
+          for (int pn = 0; pn < C::PANELS; ++pn) {
+            tma_load_4d(stage + C::C_BYTES + pn * C::PANEL_BYTES, &tmYa, BAR(B_YFULL + st), pn * 64, c0, h, b);
+            tma_load_4d(stage + C::C_BYTES + C::H_BYTES + pn * C::PANEL_BYTES, &tmYb, BAR(B_YFULL + st), pn * 64, c0, h, b);
+          }
         }
       }
       // per-column constants (the stage's previous readers are done: Y-empty is committed after the step's last MMA,
@@ -244,9 +299,11 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
         const int c = c0 + col;
         float z = 0.f, ns = 0.f, s = 0.f, nl = -INFINITY, nd = 0.f;
         if (c < p.cols_total) {
-          s = half_bits_to_f32(p.c_scale[tok_c0 + c]);
-          z = static_cast<float>(p.c_zp[tok_c0 + c]);
-          ns = -static_cast<float>(p.c_sum[tok_c0 + c]);
+          if constexpr (!REF) {
+            s = half_bits_to_f32(p.c_scale[tok_c0 + c]);
+            z = static_cast<float>(p.c_zp[tok_c0 + c]);
+            ns = -static_cast<float>(p.c_sum[tok_c0 + c]);
+          }
           nl = 0.f;
           if (KV_PASS) {
             nl = -p.lse[lse0 + c] * kLog2e;
@@ -267,11 +324,12 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
   } else if (warp == 1) {
     // ================================================================ MMA issuer (one thread)
     if (lane == 0) {
-      constexpr uint32_t kIdescT1 = make_idesc(2, 1, 1, 0, 0, 128, 128);
       constexpr uint32_t kF = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+      constexpr uint32_t kIdescT1 = REF ? make_idesc(1, kF, kF, 0, 0, 128, 128) : make_idesc(2, 1, 1, 0, 0, 128, 128);
       constexpr uint32_t kIdescT2 = make_idesc(1, kF, kF, 0, 0, 128, 128);       // both operands K-major
       constexpr uint32_t kIdescAcc = make_idesc(1, kF, kF, 0, 1, 128, D);        // B MN-major
       constexpr uint64_t kCSwz = (D == 128) ? kSwizzle128B : kSwizzle64B;
+      constexpr int kT2B = KV_PASS ? C::Y_T2B_KV : C::Y_T2B_Q;
       bool ok = mbar_wait(BAR(B_XFULL), 0, abort_flag, p.epoch);
       tc_fence_after_sync();
       for (int it = 0; it < n_steps && ok; ++it) {
@@ -280,28 +338,39 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
         ok = mbar_wait(BAR(B_YFULL + st), (it / C::STAGES) & 1, abort_flag, p.epoch);
         if (!ok) break;
         tc_fence_after_sync();
-        // T1 = Xc Yc^T (int8), T2 = Xh Ya^T (16 bit, K-major x K-major).  They overwrite the P / dS of the previous
-        // step: the tensor pipe runs MMAs in issue order, so they start after that step's accumulating MMAs
+        // T1 = Xc Yc^T (int8; REF: 16-bit tiles in their place), T2 = Xh Ya^T (16 bit, K-major x K-major).  They
+        // overwrite the P / dS of the previous step: the tensor pipe runs MMAs in issue order, so they start after
+        // that step's accumulating MMAs
         {
-          const uint64_t da = make_smem_desc(sbase + C::XC_OFF, 16, 8 * D, kCSwz);
-          const uint64_t db = make_smem_desc(stage, 16, 8 * D, kCSwz);
+          if constexpr (REF) {
 #pragma unroll
-          for (int k = 0; k < D / 32; ++k)
-            mma_i8_ss(tmem + C::T1_COL, desc_advance(da, k * 32), desc_advance(db, k * 32), kIdescT1, k > 0);
+            for (int k = 0; k < D / 16; ++k) {
+              const uint32_t off = (k / 4) * C::PANEL_BYTES + (k % 4) * 32;
+              const uint64_t ha = make_smem_desc(sbase + C::XC_OFF + off, 16, 1024, kSwizzle128B);
+              const uint64_t hb = make_smem_desc(stage + off, 16, 1024, kSwizzle128B);
+              mma_f16_ss(tmem + C::T1_COL, ha, hb, kIdescT1, k > 0);
+            }
+          } else {
+            const uint64_t da = make_smem_desc(sbase + C::XC_OFF, 16, 8 * D, kCSwz);
+            const uint64_t db = make_smem_desc(stage, 16, 8 * D, kCSwz);
+#pragma unroll
+            for (int k = 0; k < D / 32; ++k)
+              mma_i8_ss(tmem + C::T1_COL, desc_advance(da, k * 32), desc_advance(db, k * 32), kIdescT1, k > 0);
+          }
           mma_commit(BAR(B_T1));
 #pragma unroll
           for (int k = 0; k < D / 16; ++k) {
             const uint32_t off = (k / 4) * C::PANEL_BYTES + (k % 4) * 32;
             const uint64_t ha = make_smem_desc(sbase + C::XH_OFF + off, 16, 1024, kSwizzle128B);
-            const uint64_t hb = make_smem_desc(stage + C::C_BYTES + off, 16, 1024, kSwizzle128B);
+            const uint64_t hb = make_smem_desc(stage + kT2B + off, 16, 1024, kSwizzle128B);
             mma_f16_ss(tmem + C::T2_COL, ha, hb, kIdescT2, k > 0);
           }
           mma_commit(BAR(B_T2));
         }
         // accumulate with P / dS read from tensor memory, one 16-column k-step at a time as the softmax warps hand
         // the blocks over (the two column halves advance side by side)
-        const uint64_t db1 = make_smem_desc(stage + C::C_BYTES, C::PANEL_BYTES, 1024, kSwizzle128B);               // dO (pass KV)
-        const uint64_t db2 = make_smem_desc(stage + C::C_BYTES + C::H_BYTES, C::PANEL_BYTES, 1024, kSwizzle128B);  // Q^ or K^
+        const uint64_t db1 = make_smem_desc(stage + C::Y_ACC1B, C::PANEL_BYTES, 1024, kSwizzle128B);   // dO (pass KV)
+        const uint64_t db2 = make_smem_desc(stage + C::Y_ACC2B, C::PANEL_BYTES, 1024, kSwizzle128B);   // Q^ / Q or K^
 #pragma unroll
         for (int i = 0; i < C::HANDOFFS; ++i) {
           const int hf = (i & 1) * 2 + (i >> 1);           // handoff index: column half * 2 + 32-column part
@@ -345,11 +414,15 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
       rowk[k] = r0 + wq * 32 + hh * 16 + g + 8 * k;
       float A = 0.f, z = 0.f, a = 0.f, nl = -INFINITY, nd = 0.f;
       if (rowk[k] < p.rows_total) {
-        const int64_t tk = tok_r0 + rowk[k];
-        const int zi = p.r_zp[tk];
-        z = static_cast<float>(zi);
-        A = static_cast<float>(D * zi - p.r_sum[tk]);
-        a = half_bits_to_f32(p.r_scale[tk]) * p.sm_scale * kLog2e;
+        if constexpr (REF) {
+          a = p.sm_scale * kLog2e;
+        } else {
+          const int64_t tk = tok_r0 + rowk[k];
+          const int zi = p.r_zp[tk];
+          z = static_cast<float>(zi);
+          A = static_cast<float>(D * zi - p.r_sum[tk]);
+          a = half_bits_to_f32(p.r_scale[tk]) * p.sm_scale * kLog2e;
+        }
         nl = 0.f;
         if (!KV_PASS) {
           nl = -p.lse[lse0 + rowk[k]] * kLog2e;
@@ -402,8 +475,13 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
 #pragma unroll
         for (int k = 0; k < 2; ++k) { lo_b[k] = lo[k] - blk * 16; hi_b[k] = hi[k] - blk * 16; }
         uint32_t pw[4], gw[4];
-        if (masked) bwd_block<T, KV_PASS, true>(sreg[blk & 1], dreg[blk & 1], meta + blk * 20, lo_b, hi_b, rc, pw, gw);
-        else bwd_block<T, KV_PASS, false>(sreg[blk & 1], dreg[blk & 1], meta + blk * 20, lo_b, hi_b, rc, pw, gw);
+        if constexpr (REF) {
+          if (masked) bwd_block_ref<T, KV_PASS, true>(sreg[blk & 1], dreg[blk & 1], meta + blk * 20, lo_b, hi_b, rc, pw, gw);
+          else bwd_block_ref<T, KV_PASS, false>(sreg[blk & 1], dreg[blk & 1], meta + blk * 20, lo_b, hi_b, rc, pw, gw);
+        } else {
+          if (masked) bwd_block<T, KV_PASS, true>(sreg[blk & 1], dreg[blk & 1], meta + blk * 20, lo_b, hi_b, rc, pw, gw);
+          else bwd_block<T, KV_PASS, false>(sreg[blk & 1], dreg[blk & 1], meta + blk * 20, lo_b, hi_b, rc, pw, gw);
+        }
         // P / dS of this block go to 32-bit columns [8 blk, 8 blk + 8) of this half of T1 / T2: the int32 / fp32
         // values that lived there were consumed by this warp in an earlier (or this) block
         tmem_st_16x128b_x2(tT1 + blk * 8, pw);
@@ -425,6 +503,34 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
     if (ok) {
       tc_fence_after_sync();
       // this warp writes its 16 rows x D/2 columns of each accumulator
+      if (KV_PASS && p.fused) {
+        // dKV = dV + sm_scale * dK in one tensor (quant_flash_attn.py:161)
+        const uint32_t tA1 = tmem + lanes + C::ACC1_COL + ch * (D / 2), tA2 = tmem + lanes + C::ACC2_COL + ch * (D / 2);
+        T* obase = static_cast<T*>(p.out2) + b * p.out2_stride[0] + h * p.out2_stride[1] + ch * (D / 2) + 2 * q;
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          uint32_t r1[16], r2[16];
+          if (n_steps > 0) {
+            tmem_ld_16x256b_x4(tA1 + c * 32, r1);
+            tmem_ld_16x256b_x4(tA2 + c * 32, r2);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) r1[i] = r2[i] = 0u;
+          }
+#pragma unroll
+          for (int k = 0; k < 2; ++k) {
+            if (rowk[k] < p.rows_total) {
+              T* orow = obase + static_cast<int64_t>(rowk[k]) * p.out2_stride[2] + c * 32;
+#pragma unroll
+              for (int n = 0; n < 4; ++n)
+                *reinterpret_cast<uint32_t*>(orow + 8 * n) = H16::pack(
+                    __uint_as_float(r1[4 * n + 2 * k]) + p.sm_scale * __uint_as_float(r2[4 * n + 2 * k]),
+                    __uint_as_float(r1[4 * n + 2 * k + 1]) + p.sm_scale * __uint_as_float(r2[4 * n + 2 * k + 1]));
+            }
+          }
+        }
+      } else
       for (int which = KV_PASS ? 0 : 1; which < 2; ++which) {
         const uint32_t tA = tmem + lanes + (which == 0 ? C::ACC1_COL : C::ACC2_COL) + ch * (D / 2);
         const float scale = (which == 0) ? 1.0f : p.sm_scale;
@@ -464,9 +570,9 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmXc, const __grid_consta
   if (tid == 0 && *abort_flag && p.status) *p.status = QFA_STATUS_WAIT_TIMEOUT;
 }
 
-template <typename T, int D, bool KV_PASS>
+template <typename T, int D, bool KV_PASS, bool REF>
 static int launch_bwd_tc(const QfaBwdArgs& a, cudaStream_t stream) {
-  using C = BwdTcCfg<D>;
+  using C = BwdTcCfg<D, REF>;
   const CUtensorMapSwizzle cswz = (D == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   const CUtensorMapDataType hdt =
       std::is_same<T, __nv_bfloat16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -474,24 +580,38 @@ static int launch_bwd_tc(const QfaBwdArgs& a, cudaStream_t stream) {
   const QfaQuantTensor& X = KV_PASS ? a.k : a.qq;
   const QfaQuantTensor& Y = KV_PASS ? a.qq : a.k;
   const int64_t Sx = KV_PASS ? a.Skv : a.Sq, Sy = KV_PASS ? a.Sq : a.Skv;
-  const void* xh = KV_PASS ? a.v_hat : a.d_o;          // stationary 16-bit operand of T2
-  const void* ya = KV_PASS ? a.d_o : a.v_hat;          // streamed 16-bit operand of T2 (also B of acc1 in pass KV)
-  const void* yb = KV_PASS ? a.q_hat : a.k_hat;        // streamed MN-major operand of acc2
   auto map16 = [&](CUtensorMap* m, const void* base, int64_t S, const int64_t* stride_or_null) {
-    // contiguous (B,H,S,D) unless strides are given (dO)
+    // contiguous (B,H,S,D) unless strides are given (dO, Q)
     const uint64_t ss = stride_or_null ? 2ull * stride_or_null[2] : 2ull * D;
     const uint64_t sh = stride_or_null ? 2ull * stride_or_null[1] : 2ull * D * S;
     const uint64_t sb = stride_or_null ? 2ull * stride_or_null[0] : 2ull * D * S * a.H;
     return make_tmap_4d(m, base, hdt, 2, D, S, a.H, a.B, ss, sh, sb, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B);
   };
   CUtensorMap tmXc, tmXh, tmYc, tmYa, tmYb;
-  bool ok = make_tmap_4d(&tmXc, X.codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, D, Sx, a.H, a.B, X.stride[2], X.stride[1],
-                         X.stride[0], D, 128, cswz);
-  ok = ok && make_tmap_4d(&tmYc, Y.codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, D, Sy, a.H, a.B, Y.stride[2], Y.stride[1],
-                          Y.stride[0], D, 128, cswz);
-  ok = ok && map16(&tmXh, xh, Sx, KV_PASS ? nullptr : a.do_stride);
-  ok = ok && map16(&tmYa, ya, Sy, KV_PASS ? a.do_stride : nullptr);
-  ok = ok && map16(&tmYb, yb, Sy, nullptr);
+  bool ok;
+  if (REF) {
+    // K^ = V^ = a.v_hat (the dequantized K/V tensor, contiguous); Q and dO with the caller's strides
+    if (KV_PASS) {
+      ok = map16(&tmXc, a.v_hat, Sx, nullptr) && map16(&tmXh, a.v_hat, Sx, nullptr) &&
+           map16(&tmYc, a.q, Sy, a.q_stride) && map16(&tmYa, a.d_o, Sy, a.do_stride);
+    } else {
+      ok = map16(&tmXc, a.q, Sx, a.q_stride) && map16(&tmXh, a.d_o, Sx, a.do_stride) &&
+           map16(&tmYc, a.v_hat, Sy, nullptr);
+      tmYa = tmYc;
+    }
+    tmYb = tmYc;
+  } else {
+    const void* xh = KV_PASS ? a.v_hat : a.d_o;          // stationary 16-bit operand of T2
+    const void* ya = KV_PASS ? a.d_o : a.v_hat;          // streamed 16-bit operand of T2 (also B of acc1 in pass KV)
+    const void* yb = KV_PASS ? a.q_hat : a.k_hat;        // streamed MN-major operand of acc2
+    ok = make_tmap_4d(&tmXc, X.codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, D, Sx, a.H, a.B, X.stride[2], X.stride[1],
+                      X.stride[0], D, 128, cswz);
+    ok = ok && make_tmap_4d(&tmYc, Y.codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, D, Sy, a.H, a.B, Y.stride[2], Y.stride[1],
+                            Y.stride[0], D, 128, cswz);
+    ok = ok && map16(&tmXh, xh, Sx, KV_PASS ? nullptr : a.do_stride);
+    ok = ok && map16(&tmYa, ya, Sy, KV_PASS ? a.do_stride : nullptr);
+    ok = ok && map16(&tmYb, yb, Sy, nullptr);
+  }
   if (!ok) return cuda_fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
   TcBwdParams p;
   p.r_scale = X.scale; p.r_zp = X.zp; p.r_sum = X.rowsum;
@@ -507,8 +627,9 @@ static int launch_bwd_tc(const QfaBwdArgs& a, cudaStream_t stream) {
   p.rows_total = static_cast<int>(Sx);
   p.cols_total = static_cast<int>(Sy);
   p.sm_scale = a.sm_scale; p.causal = a.causal; p.status = a.status;
+  p.fused = (REF && a.dkv_fused) ? 1 : 0;
   p.epoch = next_launch_epoch();
-  auto kern = attn_bwd_tc_kernel<T, D, KV_PASS>;
+  auto kern = attn_bwd_tc_kernel<T, D, KV_PASS, REF>;
   static DeviceOnce attr_done;
   int rc = once_per_device(attr_done, [&]() -> int {
     QFA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
@@ -528,27 +649,37 @@ static int launch_bwd_tc(const QfaBwdArgs& a, cudaStream_t stream) {
 }
 
 int attn_bwd_tc_supported(const QfaBwdArgs& a) {
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (a.D != 128 && a.D != 64) return 0;
+  if (a.do_stride[0] % 8 || a.do_stride[1] % 8 || a.do_stride[2] % 8) return 0;
+  if (a.mode == QFA_MODE_REF) {
+    // the reference's operator with more than 32 query rows: fused dKV, one K/V tensor supplied dequantized (v_hat)
+    if (!a.dkv_fused || a.causal || a.Sq <= 32 || !a.q || !a.v_hat || !al(a.v_hat)) return 0;
+    if (a.k.codes != a.v.codes || a.k.scale != a.v.scale || a.k.zp != a.v.zp) return 0;
+    return 1;
+  }
   if (a.mode != QFA_MODE_INT8 || a.dkv_fused) return 0;
   if (!a.q_hat || !a.k_hat || !a.v_hat) return 0;
-  if (a.D != 128 && a.D != 64) return 0;
   if (!(a.sm_scale > 0.f)) return 0;
-  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
   if (!al(a.q_hat) || !al(a.k_hat) || !al(a.v_hat)) return 0;
-  if (a.do_stride[0] % 8 || a.do_stride[1] % 8 || a.do_stride[2] % 8) return 0;
   return 1;
+}
+
+template <typename T, int D, bool REF>
+static int bwd_tc_two_passes(const QfaBwdArgs& a, cudaStream_t stream) {
+  const int rc = launch_bwd_tc<T, D, true, REF>(a, stream);
+  if (rc) return rc;
+  return launch_bwd_tc<T, D, false, REF>(a, stream);
 }
 
 int attn_bwd_tc_entry(const QfaBwdArgs& a, cudaStream_t stream) {
   const bool bf = a.dtype == QFA_BF16;
-  int rc;
-  if (a.D == 128) {
-    rc = bf ? launch_bwd_tc<__nv_bfloat16, 128, true>(a, stream) : launch_bwd_tc<__half, 128, true>(a, stream);
-    if (rc) return rc;
-    return bf ? launch_bwd_tc<__nv_bfloat16, 128, false>(a, stream) : launch_bwd_tc<__half, 128, false>(a, stream);
+  if (a.mode == QFA_MODE_REF) {
+    if (a.D == 128) return bf ? bwd_tc_two_passes<__nv_bfloat16, 128, true>(a, stream) : bwd_tc_two_passes<__half, 128, true>(a, stream);
+    return bf ? bwd_tc_two_passes<__nv_bfloat16, 64, true>(a, stream) : bwd_tc_two_passes<__half, 64, true>(a, stream);
   }
-  rc = bf ? launch_bwd_tc<__nv_bfloat16, 64, true>(a, stream) : launch_bwd_tc<__half, 64, true>(a, stream);
-  if (rc) return rc;
-  return bf ? launch_bwd_tc<__nv_bfloat16, 64, false>(a, stream) : launch_bwd_tc<__half, 64, false>(a, stream);
+  if (a.D == 128) return bf ? bwd_tc_two_passes<__nv_bfloat16, 128, false>(a, stream) : bwd_tc_two_passes<__half, 128, false>(a, stream);
+  return bf ? bwd_tc_two_passes<__nv_bfloat16, 64, false>(a, stream) : bwd_tc_two_passes<__half, 64, false>(a, stream);
 }
 
 }  // namespace qfa

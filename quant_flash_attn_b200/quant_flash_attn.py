@@ -137,6 +137,9 @@ class QuantFlashAttention(torch.autograd.Function):
                                         ctx.PADDED_N_CTX_Q, Z, H, N_CTX_Q, HEAD_DIM, _DT[q.dtype], stream)
             _lib.check(rc, "qfa_attn_bwd_delta")
             kvq = _quant_tensor(kv_codes, kv_scale, kv_zero_point)
+            # more than 32 query rows: the tcgen05 kernels, which take the dequantized K/V tensor (rebuilt here
+            # rather than kept alive between forward and backward: one launch)
+            kv_hat = dequantize_16bit(kv_codes, kv_scale, kv_zero_point, q.dtype) if N_CTX_Q > 32 else None
             args = _lib.QfaBwdArgs(
                 mode=_lib.QFA_MODE_REF, dtype=_DT[q.dtype], causal=0, dkv_fused=1, sm_scale=float(ctx.sm_scale),
                 B=Z, H=H, Sq=N_CTX_Q, Skv=N_CTX_KV, D=HEAD_DIM,
@@ -145,7 +148,7 @@ class QuantFlashAttention(torch.autograd.Function):
                 lse_stride=ctx.PADDED_N_CTX_Q,
                 dq=dq.data_ptr(), dq_stride=_s3(dq), dk=dkv.data_ptr(), dk_stride=_s3(dkv),
                 dv=None, dv_stride=_lib.c_i64x3(0, 0, 0), dq_accum=dq_accum.data_ptr(),
-                status=_status_ptr(q.device))
+                status=_status_ptr(q.device), v_hat=kv_hat.data_ptr() if kv_hat is not None else None)
             rc = lib.qfa_attn_bwd(C.byref(args), stream)
         _lib.check(rc, "qfa_attn_bwd")
         _after_launch(q.device)
