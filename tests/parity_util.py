@@ -53,10 +53,10 @@ def close(got, want, rel=REL_TOL, cos=COS_TOL, what="", p_rounding=0.0):
     axis; channels scaled x20) pass it; everything else is held to the plain bound."""
     assert torch.isfinite(got).all(), what
     scale, raw, excess, c = measure(got, want)
-    REPORT.append({"what": what, "dtype": str(got.dtype).replace("torch.", ""), "scale": scale,
-                   "max_abs_over_scale": raw / max(scale, 1e-30),
-                   "beyond_storage_over_scale": max(excess, 0.0) / max(scale, 1e-30), "cosine": c,
-                   "bound": rel + p_rounding})
+    if scale > 1e-4:        # a result that is zero by construction has no scale to report against
+        REPORT.append({"what": what, "dtype": str(got.dtype).replace("torch.", ""), "scale": scale,
+                       "max_abs_over_scale": raw / scale, "beyond_storage_over_scale": max(excess, 0.0) / scale,
+                       "cosine": c, "bound": rel + p_rounding})
     assert excess <= (rel + p_rounding) * scale + 1e-5, \
         f"{what}: max-abs excess {excess:.3e} > {rel + p_rounding} * {scale:.3e}"
     if scale > 1e-4:
