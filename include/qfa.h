@@ -92,6 +92,7 @@ typedef struct {
   void* dequant_or_null;
   int64_t Z, H, M, D;
   int64_t sx_z, sx_h, sx_m, sx_k;
+  void* centered_or_null; /* code - zero_point as fp16, contiguous (Z, H, M, D), 16-byte aligned: QfaFwdArgs.k_ctr */
 } QfaQuantJob;
 QFA_API int qfa_quant_batch_per_token(const QfaQuantJob* jobs, int n_jobs, int dtype, qfa_stream_t stream);
 
@@ -106,6 +107,11 @@ QFA_API int qfa_dequant_per_token(const int8_t* codes, const uint16_t* scale_f16
  * One quantized operand of the attention kernels: codes (B,H,S,D) with element strides (inner
  * stride 1), and per-token scale / zero-point / code-sum arrays contiguous over (B*H*S).
  */
+/* code - zero_point as fp16 (exact), contiguous (Z, H, M, D) output; codes with strides s_z, s_h, s_m (multiples of
+ * 16), D a multiple of 16, pointers 16-byte aligned.  No counterpart in the reference: it feeds QfaFwdArgs.k_ctr. */
+QFA_API int qfa_center_per_token(const int8_t* codes, const int8_t* zp, void* out_f16,
+                                 int64_t Z, int64_t H, int64_t M, int64_t D,
+                                 int64_t s_z, int64_t s_h, int64_t s_m, qfa_stream_t stream);
 typedef struct {
   const int8_t* codes;
   int64_t stride[3];     /* batch, head, token strides of codes, in elements */
@@ -142,6 +148,12 @@ typedef struct {
    * by the tcgen05 forward (QFA_MODE_INT8 with v_hat, head dim 64 or 128); any other combination with
    * Hkv != H returns QFA_ERR_SHAPE. */
   int64_t Hkv;
+  /* Optional (QFA_MODE_INT8 with v_hat): the centered K codes, code - zero_point as fp16, contiguous
+   * (B, Hkv, Skv, D), 16-byte aligned (qfa_center_per_token, or the `centered_or_null` output of the batched
+   * quantizer).  When given, the tcgen05 forward forms the same integer dot products sum((q - z_q)(k - z_k)) with
+   * a 16-bit MMA over centered operands (exact in fp32 for D <= 128) instead of the int8 MMA plus zero-point
+   * corrections; the results agree to fp32 rounding and the kernel is faster.  NULL selects the int8 MMA. */
+  const void* k_ctr;
 } QfaFwdArgs;
 
 QFA_API int qfa_attn_fwd(const QfaFwdArgs* args, qfa_stream_t stream);

@@ -27,7 +27,8 @@ class QfaQuantJob(C.Structure):
     _fields_ = [("x", C.c_void_p), ("codes", C.c_void_p), ("scale_f16", C.c_void_p), ("zp", C.c_void_p),
                 ("rowsum_or_null", C.c_void_p), ("dequant_or_null", C.c_void_p),
                 ("Z", C.c_int64), ("H", C.c_int64), ("M", C.c_int64), ("D", C.c_int64),
-                ("sx_z", C.c_int64), ("sx_h", C.c_int64), ("sx_m", C.c_int64), ("sx_k", C.c_int64)]
+                ("sx_z", C.c_int64), ("sx_h", C.c_int64), ("sx_m", C.c_int64), ("sx_k", C.c_int64),
+                ("centered_or_null", C.c_void_p)]
 
 
 class QfaFwdArgs(C.Structure):
@@ -36,7 +37,8 @@ class QfaFwdArgs(C.Structure):
                 ("q", C.c_void_p), ("q_stride", c_i64x3),
                 ("qq", QfaQuantTensor), ("k", QfaQuantTensor), ("v", QfaQuantTensor),
                 ("v_hat", C.c_void_p), ("o", C.c_void_p), ("o_stride", c_i64x3),
-                ("lse", C.c_void_p), ("lse_stride", C.c_int64), ("status", C.c_void_p), ("Hkv", C.c_int64)]
+                ("lse", C.c_void_p), ("lse_stride", C.c_int64), ("status", C.c_void_p), ("Hkv", C.c_int64),
+                ("k_ctr", C.c_void_p)]
 
 
 class QfaBwdArgs(C.Structure):
@@ -59,6 +61,7 @@ _I64 = C.c_int64
 SIGNATURES = {
     "qfa_quant_per_token": (C.c_int, [C.c_void_p] * 5 + [_I64] * 8 + [C.c_int, C.c_void_p]),
     "qfa_quant_dequant_per_token": (C.c_int, [C.c_void_p] * 6 + [_I64] * 8 + [C.c_int, C.c_void_p]),
+    "qfa_center_per_token": (C.c_int, [C.c_void_p] * 3 + [_I64] * 7 + [C.c_void_p]),
     "qfa_quant_batch_per_token": (C.c_int, [C.POINTER(QfaQuantJob), C.c_int, C.c_int, C.c_void_p]),
     "qfa_dequant_per_token": (C.c_int, [C.c_void_p] * 4 + [_I64] * 7 + [C.c_int, C.c_void_p]),
     "qfa_attn_fwd": (C.c_int, [C.POINTER(QfaFwdArgs), C.c_void_p]),

@@ -48,17 +48,21 @@ def _quantize(x: torch.Tensor, want_sum: bool, want_dequant: bool):
     return codes, scale, zp, rowsum, xhat
 
 
-def _quantize_batch(tensors, want_dequant, outs=None):
+def _quantize_batch(tensors, want_dequant, outs=None, want_centered=None):
     """Quantizes several (B,H,S,D) tensors of one dtype on one device with a single library call (one kernel launch
     when they share the head dimension and have 16-byte aligned rows).  `want_dequant[i]` asks for the dequantized
-    copy of tensor i.  Returns one (codes, scale, zp, rowsum, dequantized-or-None) tuple per tensor, bit-identical
-    to separate `_quantize` calls.  `outs` (optional) supplies those tuples pre-allocated: codes with the strides
-    of its input, the others contiguous; nothing is allocated then."""
+    copy of tensor i, `want_centered[i]` for code - zero_point as fp16 (the K operand of the forward's 16-bit logits
+    MMA).  Returns one (codes, scale, zp, rowsum, dequantized-or-None) tuple per tensor -- with the centered tensor
+    as a sixth element where it was asked for -- bit-identical to separate `_quantize` calls.  `outs` (optional)
+    supplies those tuples pre-allocated: codes with the strides of its input, the others contiguous; nothing is
+    allocated then."""
     import ctypes as C
     x0 = tensors[0]
     jobs = (_lib.QfaQuantJob * len(tensors))()
     results, keep = [], []
-    for i, (x, dq) in enumerate(zip(tensors, want_dequant)):
+    if want_centered is None:
+        want_centered = (False,) * len(tensors)
+    for i, (x, dq, ct) in enumerate(zip(tensors, want_dequant, want_centered)):
         if x.dim() != 4:
             raise ValueError("expected a 4-D tensor (Batch, Num_Heads, Seq_Len, Head_Dim)")
         _require_cuda(x, "input_tensor")
@@ -66,8 +70,9 @@ def _quantize_batch(tensors, want_dequant, outs=None):
             raise TypeError("expected float16 or bfloat16 tensors of one dtype on one device")
         Z, H, M, K = x.shape
         if outs is not None:
-            codes, scale, zp, rowsum, xhat = outs[i]
-            if codes.stride() != x.stride() or (dq and xhat is None):
+            codes, scale, zp, rowsum, xhat = outs[i][:5]
+            ctr = outs[i][5] if len(outs[i]) > 5 else None
+            if codes.stride() != x.stride() or (dq and xhat is None) or (ct and ctr is None):
                 raise ValueError("pre-allocated quantizer outputs do not match the input")
         else:
             codes = torch.empty_like(x, dtype=torch.int8)    # the input's strides (asymmetric_quant.py:64,127)
@@ -78,10 +83,12 @@ def _quantize_batch(tensors, want_dequant, outs=None):
             zp = torch.empty(Z, H, M, 1, dtype=torch.int8, device=x.device)
             rowsum = torch.empty(Z, H, M, dtype=torch.int32, device=x.device)
             xhat = torch.empty(Z, H, M, K, dtype=x.dtype, device=x.device) if dq else None
+            ctr = torch.empty(Z, H, M, K, dtype=torch.float16, device=x.device) if ct else None
         jobs[i] = _lib.QfaQuantJob(x.data_ptr(), codes.data_ptr(), scale.data_ptr(), zp.data_ptr(), rowsum.data_ptr(),
-                                   xhat.data_ptr() if dq else None, Z, H, M, K, *x.stride())
+                                   xhat.data_ptr() if dq else None, Z, H, M, K, *x.stride(),
+                                   ctr.data_ptr() if ct else None)
         keep.append(x)
-        results.append((codes, scale, zp, rowsum, xhat))
+        results.append((codes, scale, zp, rowsum, xhat) + ((ctr,) if ct else ()))
     with torch.cuda.device(x0.device):
         rc = _lib.load().qfa_quant_batch_per_token(jobs, len(tensors), _DT[x0.dtype], _stream(x0))
     _lib.check(rc, "qfa_quant_batch_per_token")

@@ -32,6 +32,8 @@ int dequant_entry(const int8_t* codes, const uint16_t* scale, const int8_t* zp, 
                   int64_t D, int64_t sz, int64_t sh, int64_t sm, int dtype, cudaStream_t stream);
 int attn_bwd_tc_supported(const QfaBwdArgs& a);
 int attn_bwd_tc_entry(const QfaBwdArgs& a, cudaStream_t stream);
+int center_entry(const int8_t* codes, const int8_t* zp, void* out, int64_t Z, int64_t H, int64_t M, int64_t D, int64_t sz,
+                 int64_t sh, int64_t sm, cudaStream_t stream);
 int attn_fwd_mma_entry(const QfaFwdArgs& a, cudaStream_t stream);
 int attn_fwd_tc_supported(const QfaFwdArgs& a);
 int attn_fwd_tc_entry(const QfaFwdArgs& a, cudaStream_t stream);
@@ -95,6 +97,11 @@ QFA_API int qfa_dequant_per_token(const int8_t* codes, const uint16_t* scale_f16
   return dequant_entry(codes, scale_f16, zp, out, Z, H, M, D, s_z, s_h, s_m, dtype, reinterpret_cast<cudaStream_t>(stream));
 }
 
+QFA_API int qfa_center_per_token(const int8_t* codes, const int8_t* zp, void* out_f16, int64_t Z, int64_t H, int64_t M,
+                                 int64_t D, int64_t s_z, int64_t s_h, int64_t s_m, qfa_stream_t stream) {
+  return center_entry(codes, zp, out_f16, Z, H, M, D, s_z, s_h, s_m, reinterpret_cast<cudaStream_t>(stream));
+}
+
 QFA_API int qfa_attn_fwd(const QfaFwdArgs* a, qfa_stream_t stream) {
   if (!a) return QFA_ERR_NULL;
   int rc = check_common(a->mode, a->dtype, a->B, a->H, a->Sq, a->Skv, a->D);
@@ -110,6 +117,7 @@ QFA_API int qfa_attn_fwd(const QfaFwdArgs* a, qfa_stream_t stream) {
   }
   if ((rc = check_quant_tensor(a->k, a->mode == QFA_MODE_INT8))) return rc;
   if ((rc = check_quant_tensor(a->v, false))) return rc;
+  if (a->k_ctr && !aligned16(a->k_ctr)) return QFA_ERR_ALIGN;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const bool grouped = a->Hkv != 0 && a->Hkv != a->H;
   if (grouped && (a->Hkv < 0 || a->H % a->Hkv != 0)) return QFA_ERR_SHAPE;
@@ -186,7 +194,7 @@ QFA_API const char* qfa_strerror(int code) {
 }
 
 QFA_API const char* qfa_last_cuda_error(void) { return g_cuda_err; }
-QFA_API int qfa_version(void) { return 4; }
+QFA_API int qfa_version(void) { return 5; }
 QFA_API int64_t qfa_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 }  // extern "C"

@@ -1,16 +1,21 @@
 // INT8 flash-attention forward on the 5th-generation tensor cores (tcgen05) of sm_100a.
 //
-//   S  = Qc Kc^T         int8 x int8 -> int32, tcgen05.mma kind::i8, operands staged by TMA (128B/64B swizzle),
-//                        accumulator in tensor memory
-//   s  = s_q s_k (S - z_k sum(q) - z_q sum(k) + D z_q z_k) * sm_scale     fused in the softmax warps
+//   S  = sum((q - z_q)(k - z_k))   the exact integer dot product of the centered codes, by one of two routes with
+//                        bit-identical results:
+//                          int8 MMA : Qc Kc^T as int8 x int8 -> int32 (tcgen05.mma kind::i8) plus the three zero-point
+//                                     terms - z_k sum(q) - z_q sum(k) + D z_q z_k, added by the softmax warps;
+//                          centered : (Qc - z_q)(Kc - z_k)^T as fp16 x fp16 -> fp32 (kind::f16), exact because the
+//                                     operands are integers of at most 9 bits and the sums stay below 2^24
+//                        operands staged in shared memory (TMA, 128B/64B swizzle), accumulator in tensor memory
+//   s  = s_q s_k S * sm_scale      fused in the softmax warps
 //   P  = exp2(s*log2e - m), written back to tensor memory as 16-bit, aliasing S
 //   O += P V^            tcgen05.mma kind::f16 with P read from tensor memory and V^ (dequantized V, written
 //                        by the quantizer) as an MN-major shared-memory operand
 //   LSE = m + log(l)     (quant_flash_attn.py:79)
 //
 // One CTA owns two 128-row query tiles of one (batch, head) and walks over 128-token K/V tiles.
-// Warp roles: warp 0 = TMA producer (+ per-column constants), warp 1 = MMA issuer, warp 2 = tensor
-// memory allocator, warps 4-11 / 12-19 = softmax of query tile 0 / 1 (two warps per 32-lane quarter of
+// Warp roles: warp 0 = TMA producer (+ per-column constants, tensor memory allocation), warp 1 = MMA issuer,
+// warps 2-9 / 10-17 = softmax of query tile 0 / 1 (two warps per 32-lane quarter of
 // tensor memory, 16 rows each).  A softmax warp reads S in the 16x256b fragment layout (a thread owns
 // 2 rows x 32 columns), so the per-column constants are read from shared memory once per two rows,
 // row max / sum are quad shuffles, and the element-wise math
@@ -32,6 +37,7 @@ namespace qfa {
 using namespace sm100;
 
 struct TcFwdParams {
+  const int8_t* q_codes; int64_t q_stride[3];       // CTR: the softmax warps read and center the codes of Q
   const uint16_t* q_scale; const int8_t* q_zp; const int32_t* q_sum;
   const uint16_t* k_scale; const int8_t* k_zp; const int32_t* k_sum;
   void* o;
@@ -48,16 +54,26 @@ struct TcFwdParams {
 // REF = the reference's arithmetic (quant_flash_attn.py:50-79): Q stays 16-bit (scaled by sm_scale and rounded
 // in shared memory), the one dequantized K/V tensor is both operands, logits come from a 16-bit MMA in fp32; no
 // int8 tiles, no per-column constants.
-template <int D, bool REF = false>
+//
+// CTR = int8-mode arithmetic on the 16-bit tensor path.  code - zero_point lies in [-255, 255] and is exact in fp16,
+// and a dot product of D <= 128 such pairs stays below 2^24, so a `kind::f16` MMA over the CENTERED codes returns
+// the integer sum((q - z_q)(k - z_k)) exactly, as fp32: the four-term zero-point correction and the int32 -> fp32
+// step of the int8 MMA route disappear from the softmax warps (2 instead of 7 packed operations per pair of
+// logits before the exponential).  Q is centered by the softmax warps from its int8 codes while the first K/V
+// tiles arrive; K arrives centered (fp16, one extra output of the quantizer) because 16+ CTAs share each K tile.
+enum : int { kModeI8 = 0, kModeRef = 1, kModeCtr = 2 };
+
+template <int D, int MODE = kModeI8>
 struct TcCfg {
+  static constexpr bool REF = MODE == kModeRef, CTR = MODE == kModeCtr;
   static constexpr int BM = 128, BN = 128, NQT = 2;
   static constexpr int KSTAGES = REF ? 0 : 2, VSTAGES = 2, MSTAGES = REF ? 0 : 4;
-  static constexpr int Q_BYTES = BM * D * (REF ? 2 : 1); // int8 codes, or 16-bit rows as D/64 panels of 128-byte rows
-  static constexpr int K_BYTES = BN * D;                 // int8
+  static constexpr int Q_BYTES = BM * D * (MODE != kModeI8 ? 2 : 1); // int8 codes, or 16-bit rows as D/64 panels of 128-byte rows
+  static constexpr int K_BYTES = BN * D * (CTR ? 2 : 1);  // int8 codes, or (CTR) fp16 panels like a V^ tile
   static constexpr int V_BYTES = BN * D * 2;             // 16-bit
   static constexpr int V_PANELS = D / 64;                // 64-element (128-byte) column panels
   static constexpr int V_PANEL_BYTES = BN * 128;
-  static constexpr int M_BYTES = BN * 12;                // per column: z_k, -sum(k), s_k as three float arrays
+  static constexpr int M_BYTES = BN * (CTR ? 4 : 12);    // per column: z_k, -sum(k), s_k as three float arrays; CTR: s_k
   static constexpr int Q_OFF = 0;
   static constexpr int K_OFF = Q_OFF + NQT * Q_BYTES;
   static constexpr int V_OFF = K_OFF + KSTAGES * K_BYTES;
@@ -67,9 +83,12 @@ struct TcCfg {
   static constexpr int MISC_OFF = BAR_OFF + NBARS * 8;
   static constexpr int SMEM = MISC_OFF + 16 + 1024;      // + slack for 1024-byte alignment of the base
   static constexpr int SOFTMAX_THREADS = 2 * NQT * BM;   // one warp per 16 rows; a thread owns 2 rows x 32 columns
-  static constexpr int THREADS = 128 + SOFTMAX_THREADS;
-  // register budgets after the hand-over between warpgroups (setmaxnreg); see the kernel
-  static constexpr int LAUNCH_REGS = 96, CONTROL_REGS = 56, SOFTMAX_REGS = 104;
+  // Two control warps (producer, MMA issuer) and sixteen softmax warps.  Every thread keeps the 96 registers of
+  // the launch: moving registers from the control warps to the softmax warps with `setmaxnreg` (56 / 104, measured)
+  // was 4 % SLOWER -- the MMA issuer's hand-over loop is on the critical path of every K/V step and spilled at 56.
+  static constexpr int CTRL_WARPS = 2;
+  static constexpr int CTRL_THREADS = 32 * CTRL_WARPS;
+  static constexpr int THREADS = CTRL_THREADS + SOFTMAX_THREADS;
   // tensor memory columns
   static constexpr int S_COL = 0;                        // S_t at t*BN (int32), P_t aliases its first BN/2 columns
   static constexpr int O_COL = NQT * BN;                 // O_t at O_COL + t*D (fp32)
@@ -101,6 +120,35 @@ __device__ __forceinline__ void softmax_block_ref(const uint32_t (&s)[8], const 
     for (int k = 0; k < 2; ++k) {
       float2 v = make_float2(__uint_as_float(s[4 * n + 2 * k]), __uint_as_float(s[4 * n + 2 * k + 1]));
       v = __ffma2_rn(v, l2e, rc.nref2[k]);
+      if (MASKED) {
+        if (8 * n >= lim[k]) v.x = -INFINITY;
+        if (8 * n + 1 >= lim[k]) v.y = -INFINITY;
+      }
+      asm("max.f32 %0, %0, %1, %2;" : "+f"(emax[k]) : "f"(v.x), "f"(v.y));
+      if (!MAX_ONLY) {
+        const float p0 = fast_exp2(v.x), p1 = fast_exp2(v.y);
+        lsum2[k] = __fadd2_rn(lsum2[k], make_float2(p0, p1));
+        pw[2 * n + k] = H16::pack(p0, p1);            // P rounded to 16 bit (quant_flash_attn.py:75)
+      }
+    }
+  }
+}
+
+// CTR counterpart: s holds the exact integer sum((q - z_q)(k - z_k)) as fp32; `meta` points at this thread's one
+// 16-byte word of the block, s_k of its four columns.  logit*log2e - ref = (S * s_k) * a - ref.
+template <typename T, bool MASKED, bool MAX_ONLY>
+__device__ __forceinline__ void softmax_block_ctr(const uint32_t (&s)[8], const float4 x4, const int (&lim)[2],
+                                                  const RowConst2& rc, float (&emax)[2], float2 (&lsum2)[2],
+                                                  uint32_t* pw) {
+  using H16 = Half16<T>;
+#pragma unroll
+  for (int n = 0; n < 2; ++n) {
+    const float2 x2 = n ? make_float2(x4.z, x4.w) : make_float2(x4.x, x4.y);
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      float2 v = make_float2(__uint_as_float(s[4 * n + 2 * k]), __uint_as_float(s[4 * n + 2 * k + 1]));
+      v = __fmul2_rn(v, x2);
+      v = __ffma2_rn(v, rc.a2[k], rc.nref2[k]);
       if (MASKED) {
         if (8 * n >= lim[k]) v.x = -INFINITY;
         if (8 * n + 1 >= lim[k]) v.y = -INFINITY;
@@ -154,11 +202,12 @@ __device__ __forceinline__ void softmax_block(const uint32_t (&s)[8], const floa
   }
 }
 
-template <typename T, int D, bool REF>
-__global__ void __launch_bounds__(TcCfg<D, REF>::THREADS, 1)
+template <typename T, int D, int MODE>
+__global__ void __launch_bounds__(TcCfg<D, MODE>::THREADS, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const TcFwdParams p) {
-  using C = TcCfg<D, REF>;
+  using C = TcCfg<D, MODE>;
+  constexpr bool REF = C::REF, CTR = C::CTR;
   using H16 = Half16<T>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -208,7 +257,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     mbar_init(BAR(B_QSCALED), C::SOFTMAX_THREADS / 32);
     fence_barrier_init();
   }
-  if (warp == 2) {
+  if (warp == 0) {
     tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
     tmem_relinquish();
   }
@@ -217,18 +266,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp < 4) {
-  // Register hand-over between warpgroups: the control warps give registers to the softmax warps.
-  // setmaxnreg.inc BLOCKS until the CTA's pool (threads x registers the kernel was launched with) has enough
-  // free registers, so the two budgets must fit that pool or the softmax warps would wait forever; the host
-  // side refuses to launch if the compiled kernel has fewer registers per thread than LAUNCH_REGS.
-  static_assert(128 * C::CONTROL_REGS + C::SOFTMAX_THREADS * C::SOFTMAX_REGS <= C::THREADS * C::LAUNCH_REGS,
-                "setmaxnreg budgets exceed the CTA's registers");
-  static_assert(C::CONTROL_REGS == 56 && C::SOFTMAX_REGS == 104, "keep the asm immediates below in step");
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+  if (warp < C::CTRL_WARPS) {
   if (warp == 0) {
     // ================================================================ producer
-    if (lane == 0) {
+    if (lane == 0 && CTR) { prefetch_tmap(&tmK); prefetch_tmap(&tmV); }
+    if (lane == 0 && !CTR) {
       prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
       int q_tiles = 0;
       for (int t = 0; t < C::NQT; ++t) q_tiles += (n_t[t] > 0);
@@ -258,7 +300,13 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (!ok) break;
         if (lane == 0) {
           mbar_arrive_expect_tx(BAR(B_KFULL + ks), C::K_BYTES);
-          tma_load_4d(sbase + C::K_OFF + ks * C::K_BYTES, &tmK, BAR(B_KFULL + ks), 0, n0, hkv, b);
+          if constexpr (CTR) {
+            for (int pn = 0; pn < C::V_PANELS; ++pn)
+              tma_load_4d(sbase + C::K_OFF + ks * C::K_BYTES + pn * C::V_PANEL_BYTES, &tmK, BAR(B_KFULL + ks), pn * 64,
+                          n0, hkv, b);
+          } else {
+            tma_load_4d(sbase + C::K_OFF + ks * C::K_BYTES, &tmK, BAR(B_KFULL + ks), 0, n0, hkv, b);
+          }
         }
         // per-column constants z_k, -sum(k), s_k
         ok = mbar_wait(BAR(B_MEMPTY + ms), ((j / C::MSTAGES) & 1) ^ 1, abort_flag, p.epoch);
@@ -272,16 +320,22 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           float sk = 0.f, zk = 0.f, nks = 0.f;
           if (n < p.Skv) {
             sk = half_bits_to_f32(p.k_scale[tok_k0 + n]);
-            zk = static_cast<float>(p.k_zp[tok_k0 + n]);
-            nks = -static_cast<float>(p.k_sum[tok_k0 + n]);
+            if (!CTR) {
+              zk = static_cast<float>(p.k_zp[tok_k0 + n]);
+              nks = -static_cast<float>(p.k_sum[tok_k0 + n]);
+            }
           }
           // layout for the softmax threads: thread q of a quad owns columns 8n+2q, 8n+2q+1; the constants of two
-          // column groups (n even, n odd) are packed into three 16-byte words {z_k}, {-sum(k)}, {s_k}
+          // column groups (n even, n odd) are packed into three 16-byte words {z_k}, {-sum(k)}, {s_k} (CTR: {s_k})
           const int n8 = col >> 3, qq = (col >> 1) & 3, e = col & 1;
-          float* dst = meta + (((n8 >> 1) * 4 + qq) * 3) * 4 + (n8 & 1) * 2 + e;
-          dst[0] = zk;
-          dst[4] = nks;
-          dst[8] = sk;
+          if constexpr (CTR) {
+            meta[((n8 >> 1) * 4 + qq) * 4 + (n8 & 1) * 2 + e] = sk;
+          } else {
+            float* dst = meta + (((n8 >> 1) * 4 + qq) * 3) * 4 + (n8 & 1) * 2 + e;
+            dst[0] = zk;
+            dst[4] = nks;
+            dst[8] = sk;
+          }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(BAR(B_MFULL + ms));
@@ -303,17 +357,22 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     if (lane == 0) {
       constexpr uint32_t kF16Fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
       // logits: int8 x int8 -> int32, or (REF) 16-bit x 16-bit -> fp32 with both operands K-major
-      constexpr uint32_t kIdescQK = REF ? make_idesc(1, kF16Fmt, kF16Fmt, 0, 0, C::BM, C::BN) : make_idesc(2, 1, 1, 0, 0, C::BM, C::BN);
+      constexpr uint32_t kIdescQK = REF ? make_idesc(1, kF16Fmt, kF16Fmt, 0, 0, C::BM, C::BN)
+                                  : CTR ? make_idesc(1, 0, 0, 0, 0, C::BM, C::BN)       // centered codes are fp16 for both T
+                                        : make_idesc(2, 1, 1, 0, 0, C::BM, C::BN);
       constexpr uint32_t kIdescPV = make_idesc(1, kF16Fmt, kF16Fmt, 0, 1, C::BM, D);
       constexpr uint64_t kQKSwz = (D == 128) ? kSwizzle128B : kSwizzle64B;
-      bool ok = mbar_wait(BAR(B_QFULL), 0, abort_flag, p.epoch);
-      if (REF && ok) ok = mbar_wait(BAR(B_QSCALED), 0, abort_flag, p.epoch);   // Q * sm_scale, rounded, in place
+      bool ok = CTR ? true : mbar_wait(BAR(B_QFULL), 0, abort_flag, p.epoch);
+      // REF: Q * sm_scale, rounded, in place; CTR: Q codes centered into shared memory by the softmax warps
+      if ((REF || CTR) && ok) ok = mbar_wait(BAR(B_QSCALED), 0, abort_flag, p.epoch);
       tc_fence_after_sync();
 
       auto issue_qk = [&](int j, int t) {
-        if constexpr (REF) {
-          // K^ is the V^ tile of stage j (the same tensor): rows = keys, 128-byte swizzled panels of 64 columns
-          const uint32_t kv = sbase + C::V_OFF + (j % C::VSTAGES) * C::V_BYTES;
+        if constexpr (REF || CTR) {
+          // REF: K^ is the V^ tile of stage j (the same tensor); CTR: the centered K tile of its own ring.  Both:
+          // rows = keys, 128-byte swizzled panels of 64 columns
+          const uint32_t kv = CTR ? sbase + C::K_OFF + (j % (CTR ? C::KSTAGES : 1)) * C::K_BYTES
+                                  : sbase + C::V_OFF + (j % C::VSTAGES) * C::V_BYTES;
 #pragma unroll
           for (int k = 0; k < D / 16; ++k) {
             const uint32_t off = (k / 4) * C::V_PANEL_BYTES + (k % 4) * 32;
@@ -387,7 +446,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
   }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
     // ================================================================ softmax
     // One warp per 16 rows of a query tile.  S is read in the 16x256b fragment layout: thread (g, q) of the
     // warp owns rows g, g+8 of its 16-lane half and columns 8n+2q, 8n+2q+1, so the three per-column constants
@@ -395,7 +453,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     // P = exp2(logit - ref) is formed in the same pass that finds the tile max, against a reference that is
     // only raised (by a whole number: exact power-of-two rescale of O, l and P) when a tile exceeds it by
     // more than kGrow; after the first tiles that almost never happens.
-    const int sw = warp - 4;
+    const int sw = warp - C::CTRL_WARPS;
     const int t = sw >> 3;                         // query tile of this warpgroup
     const int hh = (sw >> 2) & 1;                  // which 16 lanes of the quarter
     const int wq = warp & 3;                       // tensor-memory lane quarter this warp may access
@@ -444,7 +502,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       ok = __all_sync(0xffffffffu, ok);
       if (ok) {
         uint4* qs = reinterpret_cast<uint4*>(smem + C::Q_OFF);
-        for (int c = tid - 128; c < C::NQT * C::Q_BYTES / 16; c += C::SOFTMAX_THREADS) {
+        for (int c = tid - C::CTRL_THREADS; c < C::NQT * C::Q_BYTES / 16; c += C::SOFTMAX_THREADS) {
           uint4 v = qs[c];
           float2 f;
           f = H16::unpack(v.x); v.x = H16::pack(f.x * p.sm_scale, f.y * p.sm_scale);
@@ -459,15 +517,51 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (lane == 0) mbar_arrive(BAR(B_QSCALED));
       }
     }
+    if constexpr (CTR) {
+      // Q' = q - z_q as fp16 (exact), written in the layout the 16-bit MMA reads: per tile D/64 panels of 128-byte
+      // rows, 16-byte chunks XOR-swizzled with the row number (the placement a 128-byte-swizzled TMA load would
+      // produce).  A thread converts 16 codes per turn; rows past the end of Q become zeros.
+      constexpr int CPR = D / 16;                        // 16-code chunks per row
+      const int8_t* qbase = p.q_codes + static_cast<int64_t>(b) * p.q_stride[0] + static_cast<int64_t>(h) * p.q_stride[1];
+      for (int idx = tid - C::CTRL_THREADS; idx < C::NQT * C::BM * CPR; idx += C::SOFTMAX_THREADS) {
+        const int r256 = idx / CPR, c = idx % CPR;
+        const int row = m0 + r256;
+        uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+        if (row < p.Sq) {
+          const uint4 v = __ldg(reinterpret_cast<const uint4*>(qbase + static_cast<int64_t>(row) * p.q_stride[2] + 16 * c));
+          const int z = p.q_zp[static_cast<int64_t>(bh) * p.Sq + row];
+          center4(v.x, z, lo.x, lo.y); center4(v.y, z, lo.z, lo.w); center4(v.z, z, hi.x, hi.y); center4(v.w, z, hi.z, hi.w);
+        }
+        const int t_ = r256 / C::BM, r = r256 % C::BM;
+        uint8_t* rowp = smem + C::Q_OFF + t_ * C::Q_BYTES + (c / 4) * C::V_PANEL_BYTES + r * 128;
+        const int ch = 2 * (c % 4);
+        *reinterpret_cast<uint4*>(rowp + ((ch ^ (r & 7)) << 4)) = lo;
+        *reinterpret_cast<uint4*>(rowp + (((ch + 1) ^ (r & 7)) << 4)) = hi;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(BAR(B_QSCALED));
+    }
     for (int j = 0; j < n_max && ok; ++j) {
       const int ms = REF ? 0 : j % (REF ? 1 : C::MSTAGES);
       if (j < my_n) {
         if (!REF) ok = mbar_wait(BAR(B_MFULL + ms), (j / (REF ? 1 : C::MSTAGES)) & 1, abort_flag, p.epoch);
+        const float4* meta = reinterpret_cast<const float4*>(smem + C::M_OFF + ms * C::M_BYTES) + (CTR ? 1 : 3) * q;
+        // CTR: the per-key scales of all of this thread's columns are fetched BEFORE the wait for the logits.  While
+        // the warps work on a tile the tensor core streams the other tile's operands out of shared memory at the
+        // pipe's full rate, and a load issued then waits behind that stream; issued here it completes during
+        // the wait.  (32 registers, which the packed P takes over block by block.)
+        float4 xt[C::BN / 16];
+        if constexpr (CTR) {
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+#pragma unroll
+          for (int blk = 0; blk < C::BN / 16; ++blk) xt[blk] = meta[blk * 4];
+        }
         if (ok) ok = mbar_wait(BAR(B_SFULL + t), j & 1, abort_flag, p.epoch);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after_sync();
-        const float4* meta = reinterpret_cast<const float4*>(smem + C::M_OFF + ms * C::M_BYTES) + 3 * q;
         const int n0 = j * C::BN;
         int lim[2];                                   // first masked column of each row, relative to 2q
         bool any_masked = false;
@@ -487,14 +581,18 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
         // processes the whole tile in blocks of 16 columns; the tensor-memory load of the next block is in
         // flight while the current one is computed.  MAXONLY computes only the row maxima (first tile)
-        auto run_tile = [&](auto maxonly_tag, auto masked_tag) {
+        // RELOAD (the rare recompute): the scales are read again from shared memory, block by block
+        auto run_tile = [&](auto maxonly_tag, auto masked_tag, auto reload_tag) {
           constexpr bool MAXONLY = decltype(maxonly_tag)::value;
           constexpr bool MASKED = decltype(masked_tag)::value;
+          constexpr bool RELOAD = decltype(reload_tag)::value;
           constexpr int NBLK = C::BN / 16;
           uint32_t sreg[2][8];
           tmem_ld_16x256b_x2(tS, sreg[0]);
 #pragma unroll
           for (int blk = 0; blk < NBLK; ++blk) {
+            float4 xk;
+            if constexpr (CTR) xk = RELOAD ? meta[blk * 4] : xt[blk];
             tmem_wait_ld_use(sreg[blk & 1]);
             if (blk + 1 < NBLK) tmem_ld_16x256b_x2(tS + (blk + 1) * 16, sreg[(blk + 1) & 1]);
             int lim_b[2];
@@ -502,6 +600,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             for (int k = 0; k < 2; ++k) lim_b[k] = lim[k] - blk * 16;
             if constexpr (REF)
               softmax_block_ref<T, MASKED, MAXONLY>(sreg[blk & 1], lim_b, rc, emax, lsum2, pw + blk * 4);
+            else if constexpr (CTR)
+              softmax_block_ctr<T, MASKED, MAXONLY>(sreg[blk & 1], xk, lim_b, rc, emax, lsum2, pw + blk * 4);
             else
               softmax_block<T, C::BN, MASKED, MAXONLY>(sreg[blk & 1], meta + blk * 12, lim_b, rc, emax, lsum2,
                                                        pw + blk * 4);
@@ -517,7 +617,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
         if (j == 0) {
           // no reference yet: take the exact row max of the first tile
-          if (masked) run_tile(std::true_type{}, std::true_type{}); else run_tile(std::true_type{}, std::false_type{});
+          if (masked) run_tile(std::true_type{}, std::true_type{}, std::false_type{}); else run_tile(std::true_type{}, std::false_type{}, std::false_type{});
           quad_max();
 #pragma unroll
           for (int k = 0; k < 2; ++k) {
@@ -526,7 +626,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             emax[k] = -INFINITY;
           }
         }
-        if (masked) run_tile(std::false_type{}, std::true_type{}); else run_tile(std::false_type{}, std::false_type{});
+        if (masked) run_tile(std::false_type{}, std::true_type{}, std::false_type{}); else run_tile(std::false_type{}, std::false_type{}, std::false_type{});
         quad_max();
 
         // ---- rare: some row exceeded its reference by more than 2^kGrow
@@ -577,7 +677,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             // P may have overflowed its 16-bit type: recompute the tile against the new reference
 #pragma unroll
             for (int k = 0; k < 2; ++k) { lsum2[k] = make_float2(0.f, 0.f); emax[k] = -INFINITY; }
-            run_tile(std::false_type{}, std::true_type{});
+            run_tile(std::false_type{}, std::true_type{}, std::true_type{});
           } else {
             // exact power-of-two rescale of the P already packed in registers and of its row sums
             uint32_t f2[2];
@@ -652,16 +752,17 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   // ================================================================ teardown
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 2) {
+  if (warp == 0) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, C::TMEM_COLS);
   }
   if (tid == 0 && *abort_flag && p.status) *p.status = QFA_STATUS_WAIT_TIMEOUT;
 }
 
-template <typename T, int D, bool REF>
+template <typename T, int D, int MODE>
 static int launch_tc(const QfaFwdArgs& a, cudaStream_t stream) {
-  using C = TcCfg<D, REF>;
+  using C = TcCfg<D, MODE>;
+  constexpr bool REF = C::REF, CTR = C::CTR;
   CUtensorMap tmQ, tmK, tmV;
   const CUtensorMapSwizzle qk_swz = (D == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   const CUtensorMapDataType vdt =
@@ -672,6 +773,10 @@ static int launch_tc(const QfaFwdArgs& a, cudaStream_t stream) {
     // 16-bit Q with the caller's strides, in 64-column panels; the K tensor map is not used (K^ is the V^ tile)
     ok = make_tmap_4d(&tmQ, a.q, vdt, 2, D, a.Sq, a.H, a.B, 2ull * a.q_stride[2], 2ull * a.q_stride[1],
                       2ull * a.q_stride[0], 64, C::BM, CU_TENSOR_MAP_SWIZZLE_128B);
+  } else if (CTR) {
+    // centered K: fp16 contiguous (B, Hkv, Skv, D), panels like V^; Q is not loaded by TMA in this mode
+    ok = make_tmap_4d(&tmK, a.k_ctr, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, D, a.Skv, Hkv, a.B, 2ull * D, 2ull * D * a.Skv,
+                      2ull * D * a.Skv * Hkv, 64, C::BN, CU_TENSOR_MAP_SWIZZLE_128B);
   } else {
     ok = make_tmap_4d(&tmQ, a.qq.codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, D, a.Sq, a.H, a.B, a.qq.stride[2],
                       a.qq.stride[1], a.qq.stride[0], D, C::BM, qk_swz);
@@ -681,8 +786,11 @@ static int launch_tc(const QfaFwdArgs& a, cudaStream_t stream) {
   ok = ok && make_tmap_4d(&tmV, a.v_hat, vdt, 2, D, a.Skv, Hkv, a.B, 2ull * D, 2ull * D * a.Skv,
                           2ull * D * a.Skv * Hkv, 64, C::BN, CU_TENSOR_MAP_SWIZZLE_128B);
   if (REF) tmK = tmV;
+  if (CTR) tmQ = tmK;                                  // placeholder: the kernel does not read it
   if (!ok) return cuda_fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
   TcFwdParams p;
+  p.q_codes = a.qq.codes;
+  for (int i = 0; i < 3; ++i) p.q_stride[i] = a.qq.stride[i];
   p.q_scale = a.qq.scale; p.q_zp = a.qq.zp; p.q_sum = a.qq.rowsum;
   p.k_scale = a.k.scale; p.k_zp = a.k.zp; p.k_sum = a.k.rowsum;
   p.o = a.o;
@@ -691,14 +799,10 @@ static int launch_tc(const QfaFwdArgs& a, cudaStream_t stream) {
   p.H = static_cast<int>(a.H); p.Hkv = static_cast<int>(Hkv); p.Sq = static_cast<int>(a.Sq); p.Skv = static_cast<int>(a.Skv);
   p.sm_scale = a.sm_scale; p.causal = a.causal; p.status = a.status;
   p.epoch = next_launch_epoch();
-  auto kern = attn_fwd_tc_kernel<T, D, REF>;
+  auto kern = attn_fwd_tc_kernel<T, D, MODE>;
   static DeviceOnce attr_done;
   int rc = once_per_device(attr_done, [&]() -> int {
     QFA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
-    // the register hand-over inside the kernel assumes this many registers per thread at launch
-    cudaFuncAttributes fa;
-    QFA_CUDA_TRY(cudaFuncGetAttributes(&fa, kern));
-    if (fa.numRegs < C::LAUNCH_REGS) return cuda_fail(cudaErrorLaunchOutOfResources, "forward kernel register pool");
     return QFA_OK;
   });
   if (rc != QFA_OK) return rc;
@@ -746,7 +850,7 @@ int attn_fwd_tc_supported(const QfaFwdArgs& a) {
   if (!a.v_hat) return 0;
   if (a.D != 128 && a.D != 64) return 0;
   if ((reinterpret_cast<uintptr_t>(a.v_hat) & 15) != 0) return 0;
-  if (a.mode == QFA_MODE_INT8) return a.sm_scale > 0.f ? 1 : 0;
+  if (a.mode == QFA_MODE_INT8) return a.sm_scale > 0.f ? 1 : 0;      // (k_ctr, when given, was validated by the caller)
   if (a.mode != QFA_MODE_REF || a.causal || a.Sq <= 32 || !a.q) return 0;
   if (a.k.codes != a.v.codes || a.k.scale != a.v.scale || a.k.zp != a.v.zp) return 0;
   if (a.Hkv != 0 && a.Hkv != a.H) return 0;
@@ -756,12 +860,17 @@ int attn_fwd_tc_supported(const QfaFwdArgs& a) {
 int attn_fwd_tc_entry(const QfaFwdArgs& a, cudaStream_t stream) {
   const bool bf = a.dtype == QFA_BF16;
   if (a.mode == QFA_MODE_REF) {
-    if (a.D == 128) return bf ? launch_tc<__nv_bfloat16, 128, true>(a, stream) : launch_tc<__half, 128, true>(a, stream);
-    if (a.D == 64) return bf ? launch_tc<__nv_bfloat16, 64, true>(a, stream) : launch_tc<__half, 64, true>(a, stream);
+    if (a.D == 128) return bf ? launch_tc<__nv_bfloat16, 128, kModeRef>(a, stream) : launch_tc<__half, 128, kModeRef>(a, stream);
+    if (a.D == 64) return bf ? launch_tc<__nv_bfloat16, 64, kModeRef>(a, stream) : launch_tc<__half, 64, kModeRef>(a, stream);
     return QFA_ERR_HEAD_DIM;
   }
-  if (a.D == 128) return bf ? launch_tc<__nv_bfloat16, 128, false>(a, stream) : launch_tc<__half, 128, false>(a, stream);
-  if (a.D == 64) return bf ? launch_tc<__nv_bfloat16, 64, false>(a, stream) : launch_tc<__half, 64, false>(a, stream);
+  if (a.k_ctr) {   // int8-mode arithmetic on centered fp16 operands
+    if (a.D == 128) return bf ? launch_tc<__nv_bfloat16, 128, kModeCtr>(a, stream) : launch_tc<__half, 128, kModeCtr>(a, stream);
+    if (a.D == 64) return bf ? launch_tc<__nv_bfloat16, 64, kModeCtr>(a, stream) : launch_tc<__half, 64, kModeCtr>(a, stream);
+    return QFA_ERR_HEAD_DIM;
+  }
+  if (a.D == 128) return bf ? launch_tc<__nv_bfloat16, 128, kModeI8>(a, stream) : launch_tc<__half, 128, kModeI8>(a, stream);
+  if (a.D == 64) return bf ? launch_tc<__nv_bfloat16, 64, kModeI8>(a, stream) : launch_tc<__half, 64, kModeI8>(a, stream);
   return QFA_ERR_HEAD_DIM;
 }
 

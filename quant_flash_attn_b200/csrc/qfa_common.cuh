@@ -141,6 +141,19 @@ __device__ __forceinline__ void dequant4(uint32_t packed, float zp, float scale,
   out[3] = (static_cast<float>(static_cast<int8_t>(packed >> 24)) - zp) * scale;
 }
 
+// Four int8 codes (one 32-bit word, lowest byte first) minus a zero point, as two packed fp16 pairs.  Exact:
+// byte ^ 0x80 is code + 128 as an unsigned byte, 0x6400 | byte is the fp16 number 1024 + byte, 1152 + zp <= 1279 is
+// an fp16 integer, and the difference lies in [-255, 255].
+__device__ __forceinline__ void center4(uint32_t w, int zp, uint32_t& o01, uint32_t& o23) {
+  const __half2 off = __half2half2(__int2half_rn(1152 + zp));
+  const uint32_t u = w ^ 0x80808080u;
+  const uint32_t a0 = __byte_perm(u, 0x64646464u, 0x4140), a1 = __byte_perm(u, 0x64646464u, 0x4342);
+  const __half2 h0 = __hsub2(*reinterpret_cast<const __half2*>(&a0), off);
+  const __half2 h1 = __hsub2(*reinterpret_cast<const __half2*>(&a1), off);
+  o01 = *reinterpret_cast<const uint32_t*>(&h0);
+  o23 = *reinterpret_cast<const uint32_t*>(&h1);
+}
+
 __device__ __forceinline__ float half_bits_to_f32(uint16_t bits) {
   return __half2float(__ushort_as_half(bits));
 }

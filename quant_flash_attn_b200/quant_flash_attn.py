@@ -162,10 +162,14 @@ def quantize_qkv(q, k, v):
     """Per-token quantization of the three operands of `quant_attention`.
 
     Returns three tuples (codes, scale, zp, rowsum, dequantized-or-None); only V carries the
-    dequantized 16-bit tensor (the P.V operand, quant_flash_attn.py:65-66)."""
+    dequantized 16-bit tensor (the P.V operand, quant_flash_attn.py:65-66).  The K tuple has a sixth element, the
+    centered codes (code - zero_point as fp16): with it the forward forms its exact integer logits on the 16-bit
+    tensor path; `kq[:5]` selects the int8 MMA instead (same results)."""
     if q.dtype == k.dtype == v.dtype and q.device == k.device == v.device:
-        return tuple(_quantize_batch((q, k, v), (False, False, True)))        # one launch for the three tensors
-    return _quantize(q, True, False), _quantize(k, True, False), _quantize(v, True, True)
+        # one launch for the three tensors
+        return tuple(_quantize_batch((q, k, v), (False, False, True), want_centered=(False, True, False)))
+    kq = _quantize(k, True, False)
+    return _quantize(q, True, False), kq + (center_codes(kq[0], kq[2]),), _quantize(v, True, True)
 
 
 def int8_attention_forward(qq, kq, vq, causal: bool, sm_scale: float, dtype: torch.dtype,
@@ -177,6 +181,7 @@ def int8_attention_forward(qq, kq, vq, causal: bool, sm_scale: float, dtype: tor
     kc, ks, kz, ksum = kq[:4]
     vc, vs, vz = vq[:3]
     vhat = vq[4] if len(vq) > 4 else None
+    kctr = kq[5] if len(kq) > 5 else None        # centered K codes (fp16): selects the 16-bit logits MMA
     B, H, Sq, D = qc.shape
     Hkv, Skv = kc.shape[1], kc.shape[2]
     _check_head_dim(D)
@@ -194,7 +199,8 @@ def int8_attention_forward(qq, kq, vq, causal: bool, sm_scale: float, dtype: tor
         qq=_quant_tensor(qc, qs, qz, qsum), k=_quant_tensor(kc, ks, kz, ksum), v=_quant_tensor(vc, vs, vz),
         v_hat=vhat.data_ptr() if vhat is not None else None,
         o=o.data_ptr(), o_stride=_s3(o), lse=lse.data_ptr(), lse_stride=Sq,
-        status=_status_ptr(qc.device), Hkv=Hkv)
+        status=_status_ptr(qc.device), Hkv=Hkv,
+        k_ctr=kctr.data_ptr() if (kctr is not None and vhat is not None) else None)
     with torch.cuda.device(qc.device):
         rc = _lib.load().qfa_attn_fwd(C.byref(args), _stream(qc))
     _lib.check(rc, "qfa_attn_fwd")
@@ -240,14 +246,15 @@ def quant_attention_forward(q, k, v, causal: bool, sm_scale: float, chunks: int 
     _check_head_dim(D)
     dev, dt = q.device, q.dtype
 
-    def alloc(S_, dequant):
+    def alloc(S_, dequant, centered=False):
         return (torch.empty((B, H, S_, D), dtype=torch.int8, device=dev),
                 torch.empty((B, H, S_, 1), dtype=torch.float16, device=dev),
                 torch.empty((B, H, S_, 1), dtype=torch.int8, device=dev),
                 torch.empty((B, H, S_), dtype=torch.int32, device=dev),
-                torch.empty((B, H, S_, D), dtype=dt, device=dev) if dequant else None)
+                torch.empty((B, H, S_, D), dtype=dt, device=dev) if dequant else None) + \
+               ((torch.empty((B, H, S_, D), dtype=torch.float16, device=dev),) if centered else ())
 
-    qq, kq, vq = alloc(Sq, False), alloc(Skv, False), alloc(Skv, True)
+    qq, kq, vq = alloc(Sq, False), alloc(Skv, False, True), alloc(Skv, True)
     o = torch.empty_like(q)
     lse = torch.empty((B, H, Sq), dtype=torch.float32, device=dev)
     flat = lambda t: None if t is None else t.view(1, n, *t.shape[2:])
@@ -263,12 +270,26 @@ def quant_attention_forward(q, k, v, causal: bool, sm_scale: float, chunks: int 
         side.wait_event(fork)
         with torch.cuda.stream(side):
             outs = [cut(qf), cut(kf), cut(vf)]
-            _quantize_batch([t[:, a:b] for t in xf], (False, False, True), outs=outs)
+            _quantize_batch([t[:, a:b] for t in xf], (False, False, True), outs=outs, want_centered=(False, True, False))
             int8_attention_forward(outs[0], outs[1], outs[2], causal, sm_scale, dt, o=of[:, a:b], lse=lf[:, a:b])
             done = torch.cuda.Event()
             done.record(side)
         main.wait_event(done)
     return o, lse, qq, kq, vq
+
+
+def center_codes(codes, zp) -> torch.Tensor:
+    """code - zero_point as a contiguous fp16 (B,H,S,D) tensor (exact: the difference lies in [-255, 255]): the K
+    operand of the forward's 16-bit logits MMA.  No counterpart in the reference."""
+    B, H, S, D = codes.shape
+    out = torch.empty((B, H, S, D), dtype=torch.float16, device=codes.device)
+    if codes.stride(3) != 1:
+        raise ValueError("codes must have unit stride along the head dimension")
+    with torch.cuda.device(codes.device):
+        rc = _lib.load().qfa_center_per_token(codes.data_ptr(), zp.contiguous().data_ptr(), out.data_ptr(), B, H, S, D,
+                                              codes.stride(0), codes.stride(1), codes.stride(2), _stream(codes))
+    _lib.check(rc, "qfa_center_per_token")
+    return out
 
 
 def dequantize_16bit(codes, scale, zp, dtype: torch.dtype) -> torch.Tensor:

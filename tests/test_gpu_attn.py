@@ -139,6 +139,33 @@ def test_int8_mode_forward_backward_vs_oracle(qfa, dtype, B, H, Sq, Skv, D, caus
     _close(vc.grad, dv_ref, what=tag + " dv")
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,H,Hkv,Sq,Skv,D,causal,kind", [
+    (1, 2, 2, 1000, 1000, 128, False, "outlier"), (1, 2, 2, 1000, 1000, 128, True, "normal"),
+    (1, 2, 2, 700, 700, 64, True, "loguniform"), (2, 4, 2, 300, 517, 128, False, "normal"),
+    (1, 1, 1, 77, 1290, 64, False, "outlier"), (1, 2, 1, 130, 70, 128, True, "normal"), (1, 1, 1, 1, 1, 64, False, "normal")])
+def test_two_logit_routes_give_the_same_bits(qfa, dtype, B, H, Hkv, Sq, Skv, D, causal, kind):
+    """The tcgen05 forward forms sum((q - z_q)(k - z_k)) either with the int8 MMA plus zero-point terms (K tuple
+    without the centered codes) or with the 16-bit MMA over centered operands (K tuple as quantize_qkv returns it).
+    Both are exact integer arithmetic followed by the same fp32 operations: O and LSE must be bit-identical, also
+    with grouped K/V heads, ragged tiles and the causal mask; and both must match the oracle."""
+    q = _gen((B, H, Sq, D), dtype, 51, kind)
+    k = _gen((B, Hkv, Skv, D), dtype, 52, kind)
+    v = _gen((B, Hkv, Skv, D), dtype, 53, kind)
+    sm = 1.0 / math.sqrt(D)
+    qq, kq, vq = qfa.quantize_qkv(q.cuda(), k.cuda(), v.cuda())
+    assert len(kq) == 6 and kq[5].dtype == torch.float16
+    o_c, lse_c = qfa.int8_attention_forward(qq, kq, vq, causal, sm, dtype)
+    o_i, lse_i = qfa.int8_attention_forward(qq, kq[:5], vq, causal, sm, dtype)
+    qfa.check_kernel_status()
+    assert torch.equal(o_c, o_i) and torch.equal(lse_c, lse_i)
+    if Hkv == H:
+        o_ref, lse_ref, _ = oracle.int8_mode_forward(q, k, v, causal, sm, round_output=False,
+                                                     quant=tuple(_cpu_quant(t) for t in (qq, kq, vq)))
+        _close(o_c, o_ref, what=f"int8 centered route B{B} H{H} Sq{Sq} Skv{Skv} D{D} {kind} {dtype} o".replace("torch.", ""))
+        assert (lse_c.cpu() - lse_ref).abs().max() <= 2e-3
+
+
 def test_int8_mode_lse_and_quantized_operands(qfa):
     B, H, S, D = 1, 2, 320, 128
     q, k, v = (_gen((B, H, S, D), torch.bfloat16, s, "outlier") for s in (21, 22, 23))

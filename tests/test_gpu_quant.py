@@ -212,6 +212,45 @@ def test_batched_quantizer_equals_separate_calls(qfa):
     assert lib.qfa_quant_batch_per_token(jobs, 1, 9, None) == -2
 
 
+def test_centered_codes_are_exact(qfa):
+    """The centered output (code - zero_point as fp16) of the batched quantizer -- fused into the one-launch path,
+    a second launch in the per-job fallback -- and of the standalone qfa_center_per_token all equal the integer
+    difference exactly, together with a dequantized output of the same job and for a (B,S,H,D) view."""
+    from quant_flash_attn_b200 import _lib
+    from quant_flash_attn_b200.asymmetric_quant import _quantize, _quantize_batch
+    from quant_flash_attn_b200.quant_flash_attn import center_codes
+    for dtype in (torch.bfloat16, torch.float16):
+        q = _inputs("outlier", (2, 3, 301, 128), dtype, 1).cuda()
+        k = _inputs("loguniform", (2, 77, 3, 128), dtype, 2).cuda().transpose(1, 2)
+        n0 = _lib.launch_count()
+        got = _quantize_batch((q, k, q), (False, False, True), want_centered=(False, True, True))
+        assert _lib.launch_count() - n0 == 1
+        assert len(got[0]) == 5 and len(got[1]) == 6 and len(got[2]) == 6
+        for g, x, dq in ((got[1], k, False), (got[2], q, True)):
+            w = _quantize(x, True, dq)
+            for a, b in zip(g[:5], w):
+                assert (a is None and b is None) or torch.equal(a, b)
+            want = g[0].to(torch.int32) - g[2].to(torch.int32)
+            assert g[5].dtype == torch.float16 and g[5].is_contiguous()
+            assert torch.equal(g[5].to(torch.int32), want)
+            assert torch.equal(center_codes(g[0], g[2]), g[5])
+        # per-job fallback (different head dims): quantize, then the centering kernel
+        k64 = _inputs("normal", (2, 3, 77, 64), dtype, 4).cuda()
+        n0 = _lib.launch_count()
+        got = _quantize_batch((q, k64), (False, False), want_centered=(False, True))
+        assert _lib.launch_count() - n0 == 3
+        assert torch.equal(got[1][5].to(torch.int32), got[1][0].to(torch.int32) - got[1][2].to(torch.int32))
+    # extreme codes and zero points: -128 - 127 and 127 - (-128)
+    codes = torch.tensor([-128, 127] * 32, dtype=torch.int8, device="cuda").view(1, 1, 2, 32)
+    zp = torch.tensor([127, -128], dtype=torch.int8, device="cuda").view(1, 1, 2, 1)
+    c = center_codes(codes, zp)
+    assert torch.equal(c.to(torch.int32), codes.to(torch.int32) - zp.to(torch.int32))
+    lib = _lib.load()
+    assert lib.qfa_center_per_token(None, None, None, 1, 1, 1, 16, 16, 16, 16, None) == -1
+    assert lib.qfa_center_per_token(codes.data_ptr(), zp.data_ptr(), c.data_ptr(), 1, 1, 2, 24, 48, 48, 24, None) == -4
+    assert lib.qfa_center_per_token(codes.data_ptr() + 1, zp.data_ptr(), c.data_ptr(), 1, 1, 2, 32, 64, 64, 32, None) == -6
+
+
 def test_quantizer_rejects_bad_arguments(qfa):
     with pytest.raises(RuntimeError):
         qfa.asymmetric_quant_per_token(torch.zeros(1, 1, 2, 64, dtype=torch.float16))       # CPU tensor

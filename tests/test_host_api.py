@@ -26,7 +26,7 @@ def test_library_exports_every_declared_symbol(lib):
     raw = C.CDLL(_lib.LIB_PATH)
     for name in declared:
         assert hasattr(raw, name), name
-    assert lib.qfa_version() == 4
+    assert lib.qfa_version() == 5
 
 
 def test_struct_layout_matches_header():
