@@ -727,11 +727,11 @@ def result_line(args, world, value, ms_step, ms_total, attn_ms, ops_local, launc
         "peak_kind": ("sustained" if long_run else "burst") + " bf16 dense (library GEMM), of " + peaks["source"],
         "frac_of_int8_nominal_4500": achieved / 4500.0,
         # DRAM bytes per launch: one profiler capture of the same kernel at B1 H16 (the full workload is too large
-        # to capture) read 34.55 MB + wrote 0.22 MB for 16 heads; K, V^ and Q are read once per head and O (written
-        # once) was still in L2 when that small kernel ended, so the figure is per-head reads scaled by the heads
-        # of a launch plus the output bytes
-        "traffic": n_local * (34.55e6 / 16) + n_local * S * D * 2,
-        "traffic_note": "scaled from a 16-head capture: 2.16 MB read per head + output bytes",
+        # to capture) read 42.35 MB + wrote 0.84 MB for 16 heads; the centered K (1 MB per head), V^ (1 MB) and the
+        # codes of Q (0.5 MB) are read once per head and O (written once) was still in L2 when that small kernel
+        # ended, so the figure is per-head reads scaled by the heads of a launch plus the output bytes
+        "traffic": n_local * (42.35e6 / 16) + n_local * S * D * 2,
+        "traffic_note": "scaled from a 16-head capture: 2.65 MB read per head + output bytes",
         "ms_per_launch": attn_ms,
         "timing": "CUDA events around `steps` launches of the forward alone, right after the step loop",
     }

@@ -34,8 +34,10 @@ def test_struct_layout_matches_header():
     assert C.sizeof(_lib.QfaQuantTensor) == 56
     assert _lib.QfaFwdArgs.B.offset == 16 and _lib.QfaFwdArgs.q.offset == 56
     assert _lib.QfaFwdArgs.qq.offset == 88 and _lib.QfaFwdArgs.v_hat.offset == 88 + 3 * 56
-    assert C.sizeof(_lib.QfaFwdArgs) == 88 + 3 * 56 + 8 + 8 + 24 + 8 + 8 + 8 + 8
-    assert _lib.QfaFwdArgs.Hkv.offset == C.sizeof(_lib.QfaFwdArgs) - 8
+    assert C.sizeof(_lib.QfaFwdArgs) == 88 + 3 * 56 + 8 + 8 + 24 + 8 + 8 + 8 + 8 + 8
+    assert _lib.QfaFwdArgs.Hkv.offset == C.sizeof(_lib.QfaFwdArgs) - 16
+    assert _lib.QfaFwdArgs.k_ctr.offset == C.sizeof(_lib.QfaFwdArgs) - 8
+    assert C.sizeof(_lib.QfaQuantJob) == 6 * 8 + 8 * 8 + 8 and _lib.QfaQuantJob.centered_or_null.offset == 112
     assert _lib.QfaBwdArgs.B.offset == 24 and _lib.QfaBwdArgs.qq.offset == 96
 
 
