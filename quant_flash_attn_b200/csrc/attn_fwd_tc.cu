@@ -63,10 +63,13 @@ struct TcFwdParams {
 // tiles arrive; K arrives centered (fp16, one extra output of the quantizer) because 16+ CTAs share each K tile.
 enum : int { kModeI8 = 0, kModeRef = 1, kModeCtr = 2 };
 
-template <int D, int MODE = kModeI8>
+// NQT = query tiles per CTA.  Two tiles ping-pong on one SM; with at most 128 query rows per head there is only one
+// tile, and the one-tile instantiation (half the softmax warps, tensor memory and Q buffer) lets TWO CTAs -- two
+// heads -- share an SM instead (REF mode, whose K/V ring is small enough for that).
+template <int D, int MODE = kModeI8, int NQT_ = 2>
 struct TcCfg {
   static constexpr bool REF = MODE == kModeRef, CTR = MODE == kModeCtr;
-  static constexpr int BM = 128, BN = 128, NQT = 2;
+  static constexpr int BM = 128, BN = 128, NQT = NQT_;
   static constexpr int KSTAGES = REF ? 0 : 2, VSTAGES = 2, MSTAGES = REF ? 0 : 4;
   static constexpr int Q_BYTES = BM * D * (MODE != kModeI8 ? 2 : 1); // int8 codes, or 16-bit rows as D/64 panels of 128-byte rows
   static constexpr int K_BYTES = BN * D * (CTR ? 2 : 1);  // int8 codes, or (CTR) fp16 panels like a V^ tile
@@ -92,7 +95,8 @@ struct TcCfg {
   // tensor memory columns
   static constexpr int S_COL = 0;                        // S_t at t*BN (int32), P_t aliases its first BN/2 columns
   static constexpr int O_COL = NQT * BN;                 // O_t at O_COL + t*D (fp32)
-  static constexpr int TMEM_COLS = 512;
+  static constexpr int TMEM_COLS = NQT == 2 ? 512 : 256;   // a power of two >= NQT * (BN + D)
+  static constexpr int CTAS_PER_SM = NQT == 2 ? 1 : 2;
   static constexpr uint32_t QK_SWIZZLE_ROWS_BYTES = 8 * D;    // 8 rows of D bytes per swizzle atom
 };
 
@@ -202,11 +206,11 @@ __device__ __forceinline__ void softmax_block(const uint32_t (&s)[8], const floa
   }
 }
 
-template <typename T, int D, int MODE>
-__global__ void __launch_bounds__(TcCfg<D, MODE>::THREADS, 1)
+template <typename T, int D, int MODE, int NQT>
+__global__ void __launch_bounds__(TcCfg<D, MODE, NQT>::THREADS, TcCfg<D, MODE, NQT>::CTAS_PER_SM)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const TcFwdParams p) {
-  using C = TcCfg<D, MODE>;
+  using C = TcCfg<D, MODE, NQT>;
   constexpr bool REF = C::REF, CTR = C::CTR;
   using H16 = Half16<T>;
   extern __shared__ uint8_t smem_raw[];
@@ -251,7 +255,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     for (int i = 0; i < C::MSTAGES; ++i) { mbar_init(BAR(B_MFULL + i), 1); mbar_init(BAR(B_MEMPTY + i), C::SOFTMAX_THREADS / 32); }
     for (int t = 0; t < C::NQT; ++t) {
       mbar_init(BAR(B_SFULL + t), 1);
-      mbar_init(BAR(B_PFULL + t), C::SOFTMAX_THREADS / 64);   // one arrival per softmax warp of the tile
+      mbar_init(BAR(B_PFULL + t), C::SOFTMAX_THREADS / 32 / C::NQT);   // one arrival per softmax warp of the tile
       mbar_init(BAR(B_ODONE + t), 1);
     }
     mbar_init(BAR(B_QSCALED), C::SOFTMAX_THREADS / 32);
@@ -759,9 +763,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (tid == 0 && *abort_flag && p.status) *p.status = QFA_STATUS_WAIT_TIMEOUT;
 }
 
-template <typename T, int D, int MODE>
+template <typename T, int D, int MODE, int NQT = 2>
 static int launch_tc(const QfaFwdArgs& a, cudaStream_t stream) {
-  using C = TcCfg<D, MODE>;
+  using C = TcCfg<D, MODE, NQT>;
   constexpr bool REF = C::REF, CTR = C::CTR;
   CUtensorMap tmQ, tmK, tmV;
   const CUtensorMapSwizzle qk_swz = (D == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
@@ -799,7 +803,7 @@ static int launch_tc(const QfaFwdArgs& a, cudaStream_t stream) {
   p.H = static_cast<int>(a.H); p.Hkv = static_cast<int>(Hkv); p.Sq = static_cast<int>(a.Sq); p.Skv = static_cast<int>(a.Skv);
   p.sm_scale = a.sm_scale; p.causal = a.causal; p.status = a.status;
   p.epoch = next_launch_epoch();
-  auto kern = attn_fwd_tc_kernel<T, D, MODE>;
+  auto kern = attn_fwd_tc_kernel<T, D, MODE, NQT>;
   static DeviceOnce attr_done;
   int rc = once_per_device(attr_done, [&]() -> int {
     QFA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
@@ -859,6 +863,11 @@ int attn_fwd_tc_supported(const QfaFwdArgs& a) {
 
 int attn_fwd_tc_entry(const QfaFwdArgs& a, cudaStream_t stream) {
   const bool bf = a.dtype == QFA_BF16;
+  if (a.mode == QFA_MODE_REF && a.Sq <= 128) {      // one query tile per head: two heads per SM
+    if (a.D == 128) return bf ? launch_tc<__nv_bfloat16, 128, kModeRef, 1>(a, stream) : launch_tc<__half, 128, kModeRef, 1>(a, stream);
+    if (a.D == 64) return bf ? launch_tc<__nv_bfloat16, 64, kModeRef, 1>(a, stream) : launch_tc<__half, 64, kModeRef, 1>(a, stream);
+    return QFA_ERR_HEAD_DIM;
+  }
   if (a.mode == QFA_MODE_REF) {
     if (a.D == 128) return bf ? launch_tc<__nv_bfloat16, 128, kModeRef>(a, stream) : launch_tc<__half, 128, kModeRef>(a, stream);
     if (a.D == 64) return bf ? launch_tc<__nv_bfloat16, 64, kModeRef>(a, stream) : launch_tc<__half, 64, kModeRef>(a, stream);
