@@ -38,6 +38,7 @@ using namespace sm100;
 
 struct TcFwdParams {
   const int8_t* q_codes; int64_t q_stride[3];       // CTR: the softmax warps read and center the codes of Q
+  const int8_t* kv_codes; int64_t kv_stride[3];     // RAW: the softmax warps read and dequantize the K/V codes
   const uint16_t* q_scale; const int8_t* q_zp; const int32_t* q_sum;
   const uint16_t* k_scale; const int8_t* k_zp; const int32_t* k_sum;
   void* o;
@@ -95,6 +96,10 @@ struct TcCfg {
   // tensor memory columns
   static constexpr int S_COL = 0;                        // S_t at t*BN (int32), P_t aliases its first BN/2 columns
   static constexpr int O_COL = NQT * BN;                 // O_t at O_COL + t*D (fp32)
+  // RAW (REF with one tile): the K/V tiles are dequantized inside the kernel, by the softmax warps, from the int8
+  // codes in global memory.  Every K/V tile serves a single CTA here, so a dequantized copy in HBM (2 bytes written
+  // and read per element on top of the code byte) would dominate a problem of this shape.
+  static constexpr bool RAW = REF && NQT == 1;
   static constexpr int TMEM_COLS = NQT == 2 ? 512 : 256;   // a power of two >= NQT * (BN + D)
   static constexpr int CTAS_PER_SM = NQT == 2 ? 1 : 2;
   static constexpr uint32_t QK_SWIZZLE_ROWS_BYTES = 8 * D;    // 8 rows of D bytes per swizzle atom
@@ -251,7 +256,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     *abort_flag = launch_aborted(p.epoch) ? 1 : 0;     // a CTA of this launch already gave up: drain quickly
     mbar_init(BAR(B_QFULL), 1);
     for (int i = 0; i < C::KSTAGES; ++i) { mbar_init(BAR(B_KFULL + i), 1); mbar_init(BAR(B_KEMPTY + i), 1); }
-    for (int i = 0; i < C::VSTAGES; ++i) { mbar_init(BAR(B_VFULL + i), 1); mbar_init(BAR(B_VEMPTY + i), 1); }
+    // a V stage is filled by one TMA transaction, or (RAW) by the softmax warps, one arrival each
+    for (int i = 0; i < C::VSTAGES; ++i) {
+      mbar_init(BAR(B_VFULL + i), C::RAW ? C::SOFTMAX_THREADS / 32 : 1);
+      mbar_init(BAR(B_VEMPTY + i), 1);
+    }
     for (int i = 0; i < C::MSTAGES; ++i) { mbar_init(BAR(B_MFULL + i), 1); mbar_init(BAR(B_MEMPTY + i), C::SOFTMAX_THREADS / 32); }
     for (int t = 0; t < C::NQT; ++t) {
       mbar_init(BAR(B_SFULL + t), 1);
@@ -345,6 +354,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (lane == 0) mbar_arrive(BAR(B_MFULL + ms));
       }
       if (!ok) break;
+      if constexpr (C::RAW) break;                // nothing to stream: the softmax warps fill the V stages
       // V tile (D/64 panels of 128 bytes x BN rows)
       ok = mbar_wait(BAR(B_VEMPTY + vs), ((j / C::VSTAGES) & 1) ^ 1, abort_flag, p.epoch);
       ok = __all_sync(0xffffffffu, ok);
@@ -499,6 +509,72 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     float ref[2] = {0.f, 0.f}, l_run[2] = {0.f, 0.f};
     const int my_n = n_t[t];
     bool ok = true;
+    // RAW: K^ = V^ tile `jt` = (code - zp) * fp16(scale) rounded to T (quant_flash_attn.py:65-66), from the codes in
+    // global memory into V stage jt % VSTAGES, in the 128-byte-swizzled panel layout a TMA load would produce.  The
+    // loads are issued before the wait for the stage, so they are in flight while the P.V that still reads it ends.
+    auto convert_tile = [&](int jt) -> bool {
+      constexpr int CPR = D / 16;                                   // 16-code chunks per key
+      constexpr int NCH = C::BN * CPR / C::SOFTMAX_THREADS;         // chunks per thread
+      const int vs = jt % C::VSTAGES;
+      const int hkv = h / (p.H / p.Hkv);
+      const int8_t* base = p.kv_codes + static_cast<int64_t>(b) * p.kv_stride[0] + static_cast<int64_t>(hkv) * p.kv_stride[1];
+      const int64_t tok0 = (static_cast<int64_t>(b) * p.Hkv + hkv) * p.Skv;
+      uint4 raw[NCH];
+      uint16_t sc[NCH];
+      int zp[NCH];
+#pragma unroll
+      for (int i = 0; i < NCH; ++i) {
+        const int idx = tid - C::CTRL_THREADS + i * C::SOFTMAX_THREADS;
+        const int key = jt * C::BN + idx / CPR;
+        raw[i] = make_uint4(0, 0, 0, 0); sc[i] = 0; zp[i] = 0;
+        if (key < p.Skv) {
+          raw[i] = __ldg(reinterpret_cast<const uint4*>(base + static_cast<int64_t>(key) * p.kv_stride[2] + 16 * (idx % CPR)));
+          sc[i] = p.k_scale[tok0 + key];
+          zp[i] = p.k_zp[tok0 + key];
+        }
+      }
+      bool good = mbar_wait(BAR(B_VEMPTY + vs), ((jt / C::VSTAGES) & 1) ^ 1, abort_flag, p.epoch);
+      good = __all_sync(0xffffffffu, good);
+      if (!good) return false;
+#pragma unroll
+      for (int i = 0; i < NCH; ++i) {
+        const int idx = tid - C::CTRL_THREADS + i * C::SOFTMAX_THREADS;
+        const int r = idx / CPR, c = idx % CPR;
+        uint4 lo, hi;
+        if constexpr (std::is_same<T, __half>::value) {
+          // code - zp is exact in fp16 and its product with the fp16 scale is rounded once: the same bits as the
+          // fp32 product (exact, 20 significant bits) rounded to fp16
+          const __half2 s2 = __half2half2(__ushort_as_half(sc[i]));
+          auto cv = [&](uint32_t w, uint32_t& o0, uint32_t& o1) {
+            center4(w, zp[i], o0, o1);
+            const __half2 a0 = __hmul2(*reinterpret_cast<const __half2*>(&o0), s2);
+            const __half2 a1 = __hmul2(*reinterpret_cast<const __half2*>(&o1), s2);
+            o0 = *reinterpret_cast<const uint32_t*>(&a0);
+            o1 = *reinterpret_cast<const uint32_t*>(&a1);
+          };
+          cv(raw[i].x, lo.x, lo.y); cv(raw[i].y, lo.z, lo.w); cv(raw[i].z, hi.x, hi.y); cv(raw[i].w, hi.z, hi.w);
+        } else {
+          const float sf = half_bits_to_f32(sc[i]), zf = static_cast<float>(zp[i]);
+          float f[4];
+          dequant4(raw[i].x, zf, sf, f); lo.x = H16::pack(f[0], f[1]); lo.y = H16::pack(f[2], f[3]);
+          dequant4(raw[i].y, zf, sf, f); lo.z = H16::pack(f[0], f[1]); lo.w = H16::pack(f[2], f[3]);
+          dequant4(raw[i].z, zf, sf, f); hi.x = H16::pack(f[0], f[1]); hi.y = H16::pack(f[2], f[3]);
+          dequant4(raw[i].w, zf, sf, f); hi.z = H16::pack(f[0], f[1]); hi.w = H16::pack(f[2], f[3]);
+        }
+        uint8_t* rowp = smem + C::V_OFF + vs * C::V_BYTES + (c / 4) * C::V_PANEL_BYTES + r * 128;
+        const int ch = 2 * (c % 4);
+        *reinterpret_cast<uint4*>(rowp + ((ch ^ (r & 7)) << 4)) = lo;
+        *reinterpret_cast<uint4*>(rowp + (((ch + 1) ^ (r & 7)) << 4)) = hi;
+      }
+      // generic-proxy writes must be visible to the tensor core's (async proxy) operand reads
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(BAR(B_VFULL + vs));
+      return true;
+    };
+    if constexpr (C::RAW) {
+      for (int jt = 0; jt < C::VSTAGES && jt < n_max && ok; ++jt) ok = convert_tile(jt);
+    }
     if constexpr (REF) {
       // q~ = (q * sm_scale) rounded to T (quant_flash_attn.py:52), in place in shared memory: an element-wise
       // pass does not care about the swizzled placement of the 16-byte chunks.  All sixteen warps share it.
@@ -705,6 +781,14 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(BAR(B_PFULL + t));
+        if constexpr (C::RAW) {
+          // the warps are idle now until the next logits arrive (P.V and the next Q.K^T run meanwhile): dequantize
+          // the tile after the next one into the stage this step's P.V is about to release
+          if (j + C::VSTAGES < my_n) {
+            ok = convert_tile(j + C::VSTAGES);
+            if (!ok) break;
+          }
+        }
       } else {
         // this query tile is done (causal): keep the per-column ring moving for the other tile
         if constexpr (!REF) {
@@ -787,12 +871,17 @@ static int launch_tc(const QfaFwdArgs& a, cudaStream_t stream) {
     ok = ok && make_tmap_4d(&tmK, a.k.codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, D, a.Skv, Hkv, a.B, a.k.stride[2],
                             a.k.stride[1], a.k.stride[0], D, C::BN, qk_swz);
   }
-  ok = ok && make_tmap_4d(&tmV, a.v_hat, vdt, 2, D, a.Skv, Hkv, a.B, 2ull * D, 2ull * D * a.Skv,
-                          2ull * D * a.Skv * Hkv, 64, C::BN, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (C::RAW)
+    tmV = tmQ;                                         // placeholder: the kernel dequantizes the codes itself
+  else
+    ok = ok && make_tmap_4d(&tmV, a.v_hat, vdt, 2, D, a.Skv, Hkv, a.B, 2ull * D, 2ull * D * a.Skv,
+                            2ull * D * a.Skv * Hkv, 64, C::BN, CU_TENSOR_MAP_SWIZZLE_128B);
   if (REF) tmK = tmV;
   if (CTR) tmQ = tmK;                                  // placeholder: the kernel does not read it
   if (!ok) return cuda_fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
   TcFwdParams p;
+  p.kv_codes = a.k.codes;
+  for (int i = 0; i < 3; ++i) p.kv_stride[i] = a.k.stride[i];
   p.q_codes = a.qq.codes;
   for (int i = 0; i < 3; ++i) p.q_stride[i] = a.qq.stride[i];
   p.q_scale = a.qq.scale; p.q_zp = a.qq.zp; p.q_sum = a.qq.rowsum;
@@ -847,18 +936,21 @@ int wait_timeout_selftest_entry(uint64_t budget_ns, int32_t* status, cudaStream_
 }
 
 // The tcgen05 kernel takes int8-mode problems with the dequantized V supplied by the quantizer, and REF-mode
-// problems with more than 32 query rows whose one K/V tensor is supplied dequantized (v_hat): 16-bit Q and K^ = V^
-// feed a 16-bit MMA for the logits.  (Up to 32 query rows the short-query kernels, which read the int8 codes
-// directly, are the faster path.)
+// problems with more than 32 query rows: 16-bit Q and K^ = V^ feed a 16-bit MMA for the logits.  With more than 128
+// query rows the one K/V tensor must be supplied dequantized (v_hat); up to 128 the kernel dequantizes the codes
+// itself and v_hat is ignored.  (Up to 32 query rows the short-query kernels are the faster path.)
 int attn_fwd_tc_supported(const QfaFwdArgs& a) {
-  if (!a.v_hat) return 0;
   if (a.D != 128 && a.D != 64) return 0;
-  if ((reinterpret_cast<uintptr_t>(a.v_hat) & 15) != 0) return 0;
+  if (a.mode == QFA_MODE_REF) {
+    if (a.causal || a.Sq <= 32 || !a.q) return 0;
+    if (a.k.codes != a.v.codes || a.k.scale != a.v.scale || a.k.zp != a.v.zp) return 0;
+    if (a.Hkv != 0 && a.Hkv != a.H) return 0;
+    if (a.Sq <= 128) return 1;                        // one query tile: the kernel dequantizes K/V itself
+    return (a.v_hat && (reinterpret_cast<uintptr_t>(a.v_hat) & 15) == 0) ? 1 : 0;
+  }
+  if (!a.v_hat || (reinterpret_cast<uintptr_t>(a.v_hat) & 15) != 0) return 0;
   if (a.mode == QFA_MODE_INT8) return a.sm_scale > 0.f ? 1 : 0;      // (k_ctr, when given, was validated by the caller)
-  if (a.mode != QFA_MODE_REF || a.causal || a.Sq <= 32 || !a.q) return 0;
-  if (a.k.codes != a.v.codes || a.k.scale != a.v.scale || a.k.zp != a.v.zp) return 0;
-  if (a.Hkv != 0 && a.Hkv != a.H) return 0;
-  return 1;
+  return 0;
 }
 
 int attn_fwd_tc_entry(const QfaFwdArgs& a, cudaStream_t stream) {
