@@ -67,12 +67,23 @@ enum : int { kModeI8 = 0, kModeRef = 1, kModeCtr = 2 };
 // NQT = query tiles per CTA.  Two tiles ping-pong on one SM; with at most 128 query rows per head there is only one
 // tile, and the one-tile instantiation (half the softmax warps, tensor memory and Q buffer) lets TWO CTAs -- two
 // heads -- share an SM instead (REF mode, whose K/V ring is small enough for that).
-template <int D, int MODE = kModeI8, int NQT_ = 2>
+//
+// SHORT (REF, one tile, at most 32 query rows -- the reference's own benchmark regime): only the first 32 rows of
+// the 128-row MMA tile are real.  Rows of an MMA are independent, so nothing is stored for the other 96: the Q
+// buffer holds 32 rows and the operand descriptor simply runs on into whatever follows it in shared memory; the
+// resulting logits, their "P" and their rows of O are never looked at.  That frees the shared memory for a THIRD
+// K/V stage with two CTAs per SM.  Tensor-memory lanes 0-31 are reachable from two of the eight warps only; the other
+// six have no softmax to do and become dedicated converters: decoupled from the softmax hand-overs, they stream the
+// int8 codes through a register double buffer into the stage ring, up to three tiles ahead of the MMAs.
+template <int D, int MODE = kModeI8, int NQT_ = 2, bool SHORT_ = false>
 struct TcCfg {
-  static constexpr bool REF = MODE == kModeRef, CTR = MODE == kModeCtr;
+  static constexpr bool REF = MODE == kModeRef, CTR = MODE == kModeCtr, SHORT = SHORT_;
+  static_assert(!SHORT || (REF && NQT_ == 1), "the short-query layout exists for the one-tile REF kernel only");
   static constexpr int BM = 128, BN = 128, NQT = NQT_;
-  static constexpr int KSTAGES = REF ? 0 : 2, VSTAGES = 2, MSTAGES = REF ? 0 : 4;
-  static constexpr int Q_BYTES = BM * D * (MODE != kModeI8 ? 2 : 1); // int8 codes, or 16-bit rows as D/64 panels of 128-byte rows
+  static constexpr int QROWS = SHORT ? 32 : BM;          // rows of a query tile that exist in shared memory
+  static constexpr int KSTAGES = REF ? 0 : 2, VSTAGES = SHORT ? 3 : 2, MSTAGES = REF ? 0 : 4;
+  static constexpr int Q_BYTES = QROWS * D * (MODE != kModeI8 ? 2 : 1); // int8 codes, or 16-bit rows as D/64 panels of 128-byte rows
+  static constexpr int Q_PANEL_BYTES = QROWS * 128;
   static constexpr int K_BYTES = BN * D * (CTR ? 2 : 1);  // int8 codes, or (CTR) fp16 panels like a V^ tile
   static constexpr int V_BYTES = BN * D * 2;             // 16-bit
   static constexpr int V_PANELS = D / 64;                // 64-element (128-byte) column panels
@@ -93,6 +104,8 @@ struct TcCfg {
   static constexpr int CTRL_WARPS = 2;
   static constexpr int CTRL_THREADS = 32 * CTRL_WARPS;
   static constexpr int THREADS = CTRL_THREADS + SOFTMAX_THREADS;
+  static constexpr int LIVE_WARPS = SHORT ? 2 : SOFTMAX_THREADS / 32 / NQT;   // warps of a tile that run the softmax
+  static constexpr int CONV_WARPS = SHORT ? 6 : SOFTMAX_THREADS / 32;         // warps that fill a V stage (RAW)
   // tensor memory columns
   static constexpr int S_COL = 0;                        // S_t at t*BN (int32), P_t aliases its first BN/2 columns
   static constexpr int O_COL = NQT * BN;                 // O_t at O_COL + t*D (fp32)
@@ -211,11 +224,11 @@ __device__ __forceinline__ void softmax_block(const uint32_t (&s)[8], const floa
   }
 }
 
-template <typename T, int D, int MODE, int NQT>
-__global__ void __launch_bounds__(TcCfg<D, MODE, NQT>::THREADS, TcCfg<D, MODE, NQT>::CTAS_PER_SM)
+template <typename T, int D, int MODE, int NQT, bool SHORT>
+__global__ void __launch_bounds__(TcCfg<D, MODE, NQT, SHORT>::THREADS, TcCfg<D, MODE, NQT, SHORT>::CTAS_PER_SM)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const TcFwdParams p) {
-  using C = TcCfg<D, MODE, NQT>;
+  using C = TcCfg<D, MODE, NQT, SHORT>;
   constexpr bool REF = C::REF, CTR = C::CTR;
   using H16 = Half16<T>;
   extern __shared__ uint8_t smem_raw[];
@@ -258,16 +271,16 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     for (int i = 0; i < C::KSTAGES; ++i) { mbar_init(BAR(B_KFULL + i), 1); mbar_init(BAR(B_KEMPTY + i), 1); }
     // a V stage is filled by one TMA transaction, or (RAW) by the softmax warps, one arrival each
     for (int i = 0; i < C::VSTAGES; ++i) {
-      mbar_init(BAR(B_VFULL + i), C::RAW ? C::SOFTMAX_THREADS / 32 : 1);
+      mbar_init(BAR(B_VFULL + i), C::RAW ? C::CONV_WARPS : 1);
       mbar_init(BAR(B_VEMPTY + i), 1);
     }
     for (int i = 0; i < C::MSTAGES; ++i) { mbar_init(BAR(B_MFULL + i), 1); mbar_init(BAR(B_MEMPTY + i), C::SOFTMAX_THREADS / 32); }
     for (int t = 0; t < C::NQT; ++t) {
       mbar_init(BAR(B_SFULL + t), 1);
-      mbar_init(BAR(B_PFULL + t), C::SOFTMAX_THREADS / 32 / C::NQT);   // one arrival per softmax warp of the tile
+      mbar_init(BAR(B_PFULL + t), C::LIVE_WARPS);   // one arrival per softmax warp of the tile
       mbar_init(BAR(B_ODONE + t), 1);
     }
-    mbar_init(BAR(B_QSCALED), C::SOFTMAX_THREADS / 32);
+    mbar_init(BAR(B_QSCALED), C::SHORT ? C::LIVE_WARPS : C::SOFTMAX_THREADS / 32);
     fence_barrier_init();
   }
   if (warp == 0) {
@@ -292,7 +305,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (n_t[t] == 0) continue;
         if constexpr (REF) {      // 16-bit rows: D/64 panels of 128-byte rows, like the V^ tiles
           for (int pn = 0; pn < C::V_PANELS; ++pn)
-            tma_load_4d(sbase + C::Q_OFF + t * C::Q_BYTES + pn * C::V_PANEL_BYTES, &tmQ, BAR(B_QFULL), pn * 64,
+            tma_load_4d(sbase + C::Q_OFF + t * C::Q_BYTES + pn * C::Q_PANEL_BYTES, &tmQ, BAR(B_QFULL), pn * 64,
                         m0 + t * C::BM, h, b);
         } else {
           tma_load_4d(sbase + C::Q_OFF + t * C::Q_BYTES, &tmQ, BAR(B_QFULL), 0, m0 + t * C::BM, h, b);
@@ -390,7 +403,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
           for (int k = 0; k < D / 16; ++k) {
             const uint32_t off = (k / 4) * C::V_PANEL_BYTES + (k % 4) * 32;
-            const uint64_t da = make_smem_desc(sbase + C::Q_OFF + t * C::Q_BYTES + off, 16, 1024, kSwizzle128B);
+            // (SHORT: the 128-row descriptor runs past the 32 rows of Q that exist; see TcCfg)
+            const uint32_t offa = (k / 4) * C::Q_PANEL_BYTES + (k % 4) * 32;
+            const uint64_t da = make_smem_desc(sbase + C::Q_OFF + t * C::Q_BYTES + offa, 16, 1024, kSwizzle128B);
             const uint64_t db = make_smem_desc(kv + off, 16, 1024, kSwizzle128B);
             mma_f16_ss(tmem + C::S_COL + t * C::BN, da, db, kIdescQK, k > 0);
           }
@@ -513,67 +528,115 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     // RAW: K^ = V^ tile `jt` = (code - zp) * fp16(scale) rounded to T (quant_flash_attn.py:65-66), from the codes in
     // global memory into V stage jt % VSTAGES, in the 128-byte-swizzled panel layout a TMA load would produce.  The
     // loads are issued before the wait for the stage, so they are in flight while the P.V that still reads it ends.
-    auto convert_tile = [&](int jt) -> bool {
-      constexpr int CPR = D / 16;                                   // 16-code chunks per key
-      constexpr int NCH = C::BN * CPR / C::SOFTMAX_THREADS;         // chunks per thread
-      const int vs = jt % C::VSTAGES;
-      const int hkv = h / (p.H / p.Hkv);
-      const int8_t* base = p.kv_codes + static_cast<int64_t>(b) * p.kv_stride[0] + static_cast<int64_t>(hkv) * p.kv_stride[1];
-      const int64_t tok0 = (static_cast<int64_t>(b) * p.Hkv + hkv) * p.Skv;
-      uint4 raw[NCH];
-      uint16_t sc[NCH];
-      int zp[NCH];
-#pragma unroll
-      for (int i = 0; i < NCH; ++i) {
-        const int idx = tid - C::CTRL_THREADS + i * C::SOFTMAX_THREADS;
-        const int key = jt * C::BN + idx / CPR;
-        raw[i] = make_uint4(0, 0, 0, 0); sc[i] = 0; zp[i] = 0;
-        if (key < p.Skv) {
-          raw[i] = __ldg(reinterpret_cast<const uint4*>(base + static_cast<int64_t>(key) * p.kv_stride[2] + 16 * (idx % CPR)));
-          sc[i] = p.k_scale[tok0 + key];
-          zp[i] = p.k_zp[tok0 + key];
-        }
+    constexpr int CPR = D / 16;                                     // 16-code chunks per key
+    const int hkv_c = h / (p.H / p.Hkv);
+    const int8_t* code_base = p.kv_codes + static_cast<int64_t>(b) * p.kv_stride[0] + static_cast<int64_t>(hkv_c) * p.kv_stride[1];
+    const int64_t code_tok0 = (static_cast<int64_t>(b) * p.Hkv + hkv_c) * p.Skv;
+    // chunk `idx` (key idx / CPR of the tile, codes 16 (idx % CPR) ...) of tile jt: the codes and the key's scale / zp
+    auto load_chunk = [&](int jt, int idx, uint4& raw, uint32_t& szp) {
+      const int key = jt * C::BN + idx / CPR;
+      raw = make_uint4(0, 0, 0, 0);
+      szp = 0;
+      if (key < p.Skv) {
+        raw = __ldg(reinterpret_cast<const uint4*>(code_base + static_cast<int64_t>(key) * p.kv_stride[2] + 16 * (idx % CPR)));
+        szp = static_cast<uint32_t>(p.k_scale[code_tok0 + key]) |
+              (static_cast<uint32_t>(static_cast<uint8_t>(p.k_zp[code_tok0 + key])) << 16);
       }
-      bool good = mbar_wait(BAR(B_VEMPTY + vs), ((jt / C::VSTAGES) & 1) ^ 1, abort_flag, p.epoch);
-      good = __all_sync(0xffffffffu, good);
-      if (!good) return false;
-#pragma unroll
-      for (int i = 0; i < NCH; ++i) {
-        const int idx = tid - C::CTRL_THREADS + i * C::SOFTMAX_THREADS;
-        const int r = idx / CPR, c = idx % CPR;
-        uint4 lo, hi;
-        if constexpr (std::is_same<T, __half>::value) {
-          // code - zp is exact in fp16 and its product with the fp16 scale is rounded once: the same bits as the
-          // fp32 product (exact, 20 significant bits) rounded to fp16
-          const __half2 s2 = __half2half2(__ushort_as_half(sc[i]));
-          auto cv = [&](uint32_t w, uint32_t& o0, uint32_t& o1) {
-            center4(w, zp[i], o0, o1);
-            const __half2 a0 = __hmul2(*reinterpret_cast<const __half2*>(&o0), s2);
-            const __half2 a1 = __hmul2(*reinterpret_cast<const __half2*>(&o1), s2);
-            o0 = *reinterpret_cast<const uint32_t*>(&a0);
-            o1 = *reinterpret_cast<const uint32_t*>(&a1);
-          };
-          cv(raw[i].x, lo.x, lo.y); cv(raw[i].y, lo.z, lo.w); cv(raw[i].z, hi.x, hi.y); cv(raw[i].w, hi.z, hi.w);
-        } else {
-          const float sf = half_bits_to_f32(sc[i]), zf = static_cast<float>(zp[i]);
-          float f[4];
-          dequant4(raw[i].x, zf, sf, f); lo.x = H16::pack(f[0], f[1]); lo.y = H16::pack(f[2], f[3]);
-          dequant4(raw[i].y, zf, sf, f); lo.z = H16::pack(f[0], f[1]); lo.w = H16::pack(f[2], f[3]);
-          dequant4(raw[i].z, zf, sf, f); hi.x = H16::pack(f[0], f[1]); hi.y = H16::pack(f[2], f[3]);
-          dequant4(raw[i].w, zf, sf, f); hi.z = H16::pack(f[0], f[1]); hi.w = H16::pack(f[2], f[3]);
-        }
-        uint8_t* rowp = smem + C::V_OFF + vs * C::V_BYTES + (c / 4) * C::V_PANEL_BYTES + r * 128;
-        const int ch = 2 * (c % 4);
-        *reinterpret_cast<uint4*>(rowp + ((ch ^ (r & 7)) << 4)) = lo;
-        *reinterpret_cast<uint4*>(rowp + (((ch + 1) ^ (r & 7)) << 4)) = hi;
+    };
+    // ... dequantized and stored into V stage vs (keys past the end: zeros)
+    auto store_chunk = [&](int vs, int idx, const uint4& raw, uint32_t szp) {
+      const int r = idx / CPR, c = idx % CPR;
+      const uint16_t sc = static_cast<uint16_t>(szp & 0xffffu);
+      const int zp = static_cast<int8_t>(szp >> 16);
+      uint4 lo, hi;
+      if constexpr (std::is_same<T, __half>::value) {
+        // code - zp is exact in fp16 and its product with the fp16 scale is rounded once: the same bits as the
+        // fp32 product (exact, 20 significant bits) rounded to fp16
+        const __half2 s2 = __half2half2(__ushort_as_half(sc));
+        auto cv = [&](uint32_t w, uint32_t& o0, uint32_t& o1) {
+          center4(w, zp, o0, o1);
+          const __half2 a0 = __hmul2(*reinterpret_cast<const __half2*>(&o0), s2);
+          const __half2 a1 = __hmul2(*reinterpret_cast<const __half2*>(&o1), s2);
+          o0 = *reinterpret_cast<const uint32_t*>(&a0);
+          o1 = *reinterpret_cast<const uint32_t*>(&a1);
+        };
+        cv(raw.x, lo.x, lo.y); cv(raw.y, lo.z, lo.w); cv(raw.z, hi.x, hi.y); cv(raw.w, hi.z, hi.w);
+      } else {
+        const float sf = half_bits_to_f32(sc), zf = static_cast<float>(zp);
+        float f[4];
+        dequant4(raw.x, zf, sf, f); lo.x = H16::pack(f[0], f[1]); lo.y = H16::pack(f[2], f[3]);
+        dequant4(raw.y, zf, sf, f); lo.z = H16::pack(f[0], f[1]); lo.w = H16::pack(f[2], f[3]);
+        dequant4(raw.z, zf, sf, f); hi.x = H16::pack(f[0], f[1]); hi.y = H16::pack(f[2], f[3]);
+        dequant4(raw.w, zf, sf, f); hi.z = H16::pack(f[0], f[1]); hi.w = H16::pack(f[2], f[3]);
       }
+      uint8_t* rowp = smem + C::V_OFF + vs * C::V_BYTES + (c / 4) * C::V_PANEL_BYTES + r * 128;
+      const int ch = 2 * (c % 4);
+      *reinterpret_cast<uint4*>(rowp + ((ch ^ (r & 7)) << 4)) = lo;
+      *reinterpret_cast<uint4*>(rowp + (((ch + 1) ^ (r & 7)) << 4)) = hi;
+    };
+    // the stage is complete as far as this warp is concerned
+    auto publish_stage = [&](int vs) {
       // generic-proxy writes must be visible to the tensor core's (async proxy) operand reads
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(BAR(B_VFULL + vs));
+    };
+    auto wait_stage_free = [&](int jt) -> bool {
+      bool good = mbar_wait(BAR(B_VEMPTY + jt % C::VSTAGES), ((jt / C::VSTAGES) & 1) ^ 1, abort_flag, p.epoch);
+      return __all_sync(0xffffffffu, good);
+    };
+    // all softmax warps share the conversion of a tile (the one-tile kernel with 33 to 128 query rows)
+    auto convert_tile = [&](int jt) -> bool {
+      constexpr int NCH = C::BN * CPR / C::SOFTMAX_THREADS;         // chunks per thread
+      uint4 raw[NCH];
+      uint32_t szp[NCH];
+#pragma unroll
+      for (int i = 0; i < NCH; ++i) load_chunk(jt, tid - C::CTRL_THREADS + i * C::SOFTMAX_THREADS, raw[i], szp[i]);
+      if (!wait_stage_free(jt)) return false;
+#pragma unroll
+      for (int i = 0; i < NCH; ++i) store_chunk(jt % C::VSTAGES, tid - C::CTRL_THREADS + i * C::SOFTMAX_THREADS, raw[i], szp[i]);
+      publish_stage(jt % C::VSTAGES);
       return true;
     };
-    if constexpr (C::RAW) {
+    if constexpr (C::SHORT) {
+      if (wq != 0) {
+        // ---------------- dedicated converter warp (tensor-memory lanes 0-31 are out of its reach): walks the K/V
+        // tiles on its own, paced only by the release of the stages, one tile of codes in registers ahead
+        const int crank = sw - (sw > 2 ? 1 : 0) - (sw > 6 ? 1 : 0);          // 0..5 among the converter warps
+        const int ctid = crank * 32 + lane;
+        constexpr int CTHREADS = C::CONV_WARPS * 32;
+        constexpr int NSLOT = (C::BN * CPR + CTHREADS - 1) / CTHREADS;
+        uint4 rawA[NSLOT], rawB[NSLOT];
+        uint32_t szA[NSLOT], szB[NSLOT];
+        auto issue = [&](int jt, uint4 (&raw)[NSLOT], uint32_t (&szp)[NSLOT]) {
+#pragma unroll
+          for (int i = 0; i < NSLOT; ++i) {
+            const int idx = ctid + i * CTHREADS;
+            if (idx < C::BN * CPR) load_chunk(jt, idx, raw[i], szp[i]);
+          }
+        };
+        auto emit = [&](int jt, const uint4 (&raw)[NSLOT], const uint32_t (&szp)[NSLOT]) -> bool {
+          if (!wait_stage_free(jt)) return false;
+#pragma unroll
+          for (int i = 0; i < NSLOT; ++i) {
+            const int idx = ctid + i * CTHREADS;
+            if (idx < C::BN * CPR) store_chunk(jt % C::VSTAGES, idx, raw[i], szp[i]);
+          }
+          publish_stage(jt % C::VSTAGES);
+          return true;
+        };
+        if (n_max > 0) issue(0, rawA, szA);
+        for (int jt = 0; jt < n_max && ok; jt += 2) {
+          if (jt + 1 < n_max) issue(jt + 1, rawB, szB);
+          ok = emit(jt, rawA, szA);
+          if (!ok || jt + 1 >= n_max) break;
+          if (jt + 2 < n_max) issue(jt + 2, rawA, szA);
+          ok = emit(jt + 1, rawB, szB);
+        }
+      }
+    }
+    if (!(C::SHORT && wq != 0)) {
+    if constexpr (C::RAW && !C::SHORT) {
       for (int jt = 0; jt < C::VSTAGES && jt < n_max && ok; ++jt) ok = convert_tile(jt);
     }
     if constexpr (REF) {
@@ -583,7 +646,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       ok = __all_sync(0xffffffffu, ok);
       if (ok) {
         uint4* qs = reinterpret_cast<uint4*>(smem + C::Q_OFF);
-        for (int c = tid - C::CTRL_THREADS; c < C::NQT * C::Q_BYTES / 16; c += C::SOFTMAX_THREADS) {
+        // (SHORT: the two softmax warps alone; the converters are already streaming codes)
+        const int c0 = C::SHORT ? hh * 32 + lane : tid - C::CTRL_THREADS;
+        constexpr int cstep = C::SHORT ? C::LIVE_WARPS * 32 : C::SOFTMAX_THREADS;
+        for (int c = c0; c < C::NQT * C::Q_BYTES / 16; c += cstep) {
           uint4 v = qs[c];
           float2 f;
           f = H16::unpack(v.x); v.x = H16::pack(f.x * p.sm_scale, f.y * p.sm_scale);
@@ -614,7 +680,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           center4(v.x, z, lo.x, lo.y); center4(v.y, z, lo.z, lo.w); center4(v.z, z, hi.x, hi.y); center4(v.w, z, hi.z, hi.w);
         }
         const int t_ = r256 / C::BM, r = r256 % C::BM;
-        uint8_t* rowp = smem + C::Q_OFF + t_ * C::Q_BYTES + (c / 4) * C::V_PANEL_BYTES + r * 128;
+        uint8_t* rowp = smem + C::Q_OFF + t_ * C::Q_BYTES + (c / 4) * C::Q_PANEL_BYTES + r * 128;
         const int ch = 2 * (c % 4);
         *reinterpret_cast<uint4*>(rowp + ((ch ^ (r & 7)) << 4)) = lo;
         *reinterpret_cast<uint4*>(rowp + (((ch + 1) ^ (r & 7)) << 4)) = hi;
@@ -650,7 +716,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(BAR(B_PFULL + t));
-          if (j + C::VSTAGES < my_n) {
+          if (!C::SHORT && j + C::VSTAGES < my_n) {
             ok = convert_tile(j + C::VSTAGES);
             if (!ok) break;
           }
@@ -795,7 +861,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(BAR(B_PFULL + t));
-        if constexpr (C::RAW) {
+        if constexpr (C::RAW && !C::SHORT) {
           // the warps are idle now until the next logits arrive (P.V and the next Q.K^T run meanwhile): dequantize
           // the tile after the next one into the stage this step's P.V is about to release
           if (j + C::VSTAGES < my_n) {
@@ -849,6 +915,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
       }
     }
+    }   // softmax (not converter) warps
   }
 
   // ================================================================ teardown
@@ -861,9 +928,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (tid == 0 && *abort_flag && p.status) *p.status = QFA_STATUS_WAIT_TIMEOUT;
 }
 
-template <typename T, int D, int MODE, int NQT = 2>
+template <typename T, int D, int MODE, int NQT = 2, bool SHORT = false>
 static int launch_tc(const QfaFwdArgs& a, cudaStream_t stream) {
-  using C = TcCfg<D, MODE, NQT>;
+  using C = TcCfg<D, MODE, NQT, SHORT>;
   constexpr bool REF = C::REF, CTR = C::CTR;
   CUtensorMap tmQ, tmK, tmV;
   const CUtensorMapSwizzle qk_swz = (D == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
@@ -874,7 +941,7 @@ static int launch_tc(const QfaFwdArgs& a, cudaStream_t stream) {
   if (REF) {
     // 16-bit Q with the caller's strides, in 64-column panels; the K tensor map is not used (K^ is the V^ tile)
     ok = make_tmap_4d(&tmQ, a.q, vdt, 2, D, a.Sq, a.H, a.B, 2ull * a.q_stride[2], 2ull * a.q_stride[1],
-                      2ull * a.q_stride[0], 64, C::BM, CU_TENSOR_MAP_SWIZZLE_128B);
+                      2ull * a.q_stride[0], 64, C::QROWS, CU_TENSOR_MAP_SWIZZLE_128B);
   } else if (CTR) {
     // centered K: fp16 contiguous (B, Hkv, Skv, D), panels like V^; Q is not loaded by TMA in this mode
     ok = make_tmap_4d(&tmK, a.k_ctr, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, D, a.Skv, Hkv, a.B, 2ull * D, 2ull * D * a.Skv,
@@ -906,7 +973,7 @@ static int launch_tc(const QfaFwdArgs& a, cudaStream_t stream) {
   p.H = static_cast<int>(a.H); p.Hkv = static_cast<int>(Hkv); p.Sq = static_cast<int>(a.Sq); p.Skv = static_cast<int>(a.Skv);
   p.sm_scale = a.sm_scale; p.causal = a.causal; p.status = a.status;
   p.epoch = next_launch_epoch();
-  auto kern = attn_fwd_tc_kernel<T, D, MODE, NQT>;
+  auto kern = attn_fwd_tc_kernel<T, D, MODE, NQT, SHORT>;
   static DeviceOnce attr_done;
   int rc = once_per_device(attr_done, [&]() -> int {
     QFA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
@@ -950,15 +1017,15 @@ int wait_timeout_selftest_entry(uint64_t budget_ns, int32_t* status, cudaStream_
 }
 
 // The tcgen05 kernel takes int8-mode problems with the dequantized V supplied by the quantizer, and REF-mode
-// problems with at least 32 query rows: 16-bit Q and K^ = V^ feed a 16-bit MMA for the logits.  With more than 128
+// problems with more than 16 query rows: 16-bit Q and K^ = V^ feed a 16-bit MMA for the logits.  With more than 128
 // query rows the one K/V tensor must be supplied dequantized (v_hat); up to 128 the kernel dequantizes the codes
-// itself and v_hat is ignored.  (Below 32 query rows the short-query kernels are the faster path.)
+// itself and v_hat is ignored.  (Up to 16 query rows the short-query kernels are the faster path.)
 int attn_fwd_tc_supported(const QfaFwdArgs& a) {
   if (a.D != 128 && a.D != 64) return 0;
   if (a.mode == QFA_MODE_REF) {
-    // below 32 query rows the short-query kernels are faster (measured at 16 rows: 1.17 against 1.63 ms; at 32 rows
-    // this kernel wins, 0.91 against 1.06 ms)
-    if (a.causal || a.Sq < 32 || !a.q) return 0;
+    // Up to 16 query rows the mma.sync short-query kernels are as fast or faster (Z256 H16 NKV4096 D128 at 16 rows:
+    // 1.17 ms against 1.23 ms here); from 17 rows on this kernel wins (32 rows: 0.70 against 1.06 ms).
+    if (a.causal || a.Sq <= 16 || !a.q) return 0;
     if (a.k.codes != a.v.codes || a.k.scale != a.v.scale || a.k.zp != a.v.zp) return 0;
     if (a.Hkv != 0 && a.Hkv != a.H) return 0;
     if (a.Sq <= 128) return 1;                        // one query tile: the kernel dequantizes K/V itself
@@ -971,6 +1038,11 @@ int attn_fwd_tc_supported(const QfaFwdArgs& a) {
 
 int attn_fwd_tc_entry(const QfaFwdArgs& a, cudaStream_t stream) {
   const bool bf = a.dtype == QFA_BF16;
+  if (a.mode == QFA_MODE_REF && a.Sq <= 32) {      // at most 32 query rows: dedicated converter warps, three K/V stages
+    if (a.D == 128) return bf ? launch_tc<__nv_bfloat16, 128, kModeRef, 1, true>(a, stream) : launch_tc<__half, 128, kModeRef, 1, true>(a, stream);
+    if (a.D == 64) return bf ? launch_tc<__nv_bfloat16, 64, kModeRef, 1, true>(a, stream) : launch_tc<__half, 64, kModeRef, 1, true>(a, stream);
+    return QFA_ERR_HEAD_DIM;
+  }
   if (a.mode == QFA_MODE_REF && a.Sq <= 128) {      // one query tile per head: two heads per SM
     if (a.D == 128) return bf ? launch_tc<__nv_bfloat16, 128, kModeRef, 1>(a, stream) : launch_tc<__half, 128, kModeRef, 1>(a, stream);
     if (a.D == 64) return bf ? launch_tc<__nv_bfloat16, 64, kModeRef, 1>(a, stream) : launch_tc<__half, 64, kModeRef, 1>(a, stream);

@@ -99,8 +99,8 @@ class QuantFlashAttention(torch.autograd.Function):
 
         kvq = _quant_tensor(kv_codes_k, kv_scale_k, kv_zp_k)
         # more than 128 query rows: the tcgen05 kernel takes the K/V tensor dequantized to 16 bit ((code - zp) * scale
-        # rounded to q's dtype, quant_flash_attn.py:65-66) as both of its operands; 32 to 128 rows: one query tile per
-        # head, every K/V tile is read once and the kernel dequantizes the codes itself; below 32 rows the
+        # rounded to q's dtype, quant_flash_attn.py:65-66) as both of its operands; 17 to 128 rows: one query tile per
+        # head, every K/V tile is read once and the kernel dequantizes the codes itself; up to 16 rows the
         # short-query kernels read the int8 codes
         kv_hat = dequantize_16bit(kv_codes_k, kv_scale_k, kv_zp_k, q.dtype) if N_CTX_Q > 128 else None
         args = _lib.QfaFwdArgs(
