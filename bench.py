@@ -502,9 +502,9 @@ def single_gpu_extras(qfa, extra, runner, dev, stream, sm):
     # against a long per-token-quantized K=V, ref mode, forward and backward.  HBM-bound on the int8 codes:
     # algorithmic bytes = NKV * (D + 3) per head read once (+ Q, O), reported against the measured copy bandwidth
     sq = []
-    # (the shapes with 64 to 128 query rows run on the one-tile tcgen05 forward, which dequantizes K/V in the kernel)
+    # (the shapes with 17 to 128 query rows run on the one-tile tcgen05 forward, which dequantizes K/V in the kernel)
     for (z, hh, nq, nkv, dd) in ((256, 16, 16, 1024, 128), (256, 16, 16, 4096, 128), (64, 16, 16, 4096, 64),
-                                 (64, 16, 64, 2048, 128), (99, 53, 97, 689, 128), (64, 16, 128, 2048, 128),
+                                 (256, 16, 32, 2048, 128), (64, 16, 64, 2048, 128), (99, 53, 97, 689, 128), (64, 16, 128, 2048, 128),
                                  (64, 16, 128, 4096, 64)):
         rq = torch.randn(z, hh, nq, dd, device=dev, dtype=torch.float16, requires_grad=True)
         rkv = torch.randn(z, hh, nkv, dd, device=dev, dtype=torch.float16, requires_grad=True)
