@@ -57,7 +57,11 @@ def test_ref_mode_vs_reference_fixtures(qfa, path):
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("shape", [(1, 2, 17, 1023, 128), (2, 3, 18, 512, 64), (1, 2, 97, 689, 128),
-                                   (1, 1, 200, 130, 64), (1, 2, 1, 64, 128), (1, 1, 64, 1, 64)])
+                                   (1, 1, 200, 130, 64), (1, 2, 1, 64, 128), (1, 1, 64, 1, 64),
+                                   # 17 to 32 query rows (dedicated converter warps, three K/V stages): one, two and
+                                   # many K/V tiles, ragged last tile; 33 to 128 rows with exactly two and three tiles
+                                   (1, 1, 32, 1, 64), (1, 2, 20, 130, 128), (2, 2, 31, 257, 64), (1, 2, 25, 640, 128),
+                                   (1, 2, 128, 256, 128), (1, 1, 33, 384, 64)])
 def test_ref_mode_vs_oracle_ragged(qfa, dtype, shape):
     Z, H, NQ, NKV, D = shape
     q = _gen((Z, H, NQ, D), dtype, 1)
