@@ -127,7 +127,9 @@ typedef struct {
  * QFA_MODE_REF : q (16-bit) is read, `qq` is ignored.  k and v may be the same tensor.
  * QFA_MODE_INT8: qq, k (codes + scale + zp + rowsum) feed the int8 MMA; q is ignored.
  * v_hat (optional, 16-bit, contiguous (B,H,Skv,D)): dequantized V as written by
- * qfa_quant_dequant_per_token; when NULL the kernel dequantizes v's codes itself.
+ * qfa_quant_dequant_per_token; when NULL the kernel dequantizes v's codes itself.  It selects the tcgen05 kernels:
+ * QFA_MODE_INT8 always needs it for them; QFA_MODE_REF (k and v the same tensor, non-causal) needs it with more than
+ * 128 query rows only -- with 17 to 128 rows the tcgen05 kernel dequantizes the codes itself and ignores v_hat.
  * o: 16-bit (B,H,Sq,D) with strides; lse: fp32, row b*H+h starts at lse + (b*H+h)*lse_stride.
  */
 typedef struct {
