@@ -2,7 +2,7 @@
 """Benchmark of the quantized-attention hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--scaling strong|weak]
-    python bench.py --profile-case quant|fwd|fwd_causal|bwd|shortq|midq     (small fixed case for a profiler capture)
+    python bench.py --profile-case quant|fwd|fwd_causal|bwd|shortq|q32|midq     (small fixed case for a profiler capture)
 
 Workload: INT8 attention forward at B=4 H=32 S=4096 D=128, bf16 inputs ~N(0,1) with 1 % of the channels scaled
 x20, seeded per (batch, head), non-causal.  One step = quantize Q, K, V per token (the batched quantizer, V also
@@ -788,10 +788,10 @@ def run_profile_case(case: str):
         torch.cuda.synchronize()
         print("ok", int(out[3].sum()))
         return
-    if case in ("shortq", "midq"):
+    if case in ("shortq", "q32", "midq"):
         # the reference's own regime (test_speed.py:69-77) at a quarter of its batch: Z64 H16 NQ16 NKV2048 D128 fp16;
-        # "midq": 128 query rows, the one-tile tcgen05 forward that dequantizes K/V inside the kernel
-        z, hh, nq, nkv, dd = 64, 16, (16 if case == "shortq" else 128), 2048, 128
+        # "midq" / "q32": 128 / 32 query rows, the one-tile tcgen05 forwards that dequantize K/V inside the kernel
+        z, hh, nq, nkv, dd = 64, 16, {"shortq": 16, "q32": 32, "midq": 128}[case], 2048, 128
         q = torch.randn(z, hh, nq, dd, device=dev, dtype=torch.float16, requires_grad=True)
         kv = torch.randn(z, hh, nkv, dd, device=dev, dtype=torch.float16, requires_grad=True)
         go = torch.randn_like(q)
@@ -828,7 +828,7 @@ def main():
                     help="with --gpus N > 1: partition the fixed workload (strong) or replicate it per GPU (weak)")
     ap.add_argument("--skip-extras", action="store_true", help="only the timed step loop and the end-to-end leg")
     ap.add_argument("--eager", action="store_true", help="launch every step eagerly instead of replaying CUDA graphs")
-    ap.add_argument("--profile-case", default=None, choices=["quant", "fwd", "fwd_causal", "bwd", "shortq", "midq"])
+    ap.add_argument("--profile-case", default=None, choices=["quant", "fwd", "fwd_causal", "bwd", "shortq", "q32", "midq"])
     args = ap.parse_args()
     StepGraphs.eager_only = args.eager
     if args.profile_case:
