@@ -532,20 +532,26 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int hkv_c = h / (p.H / p.Hkv);
     const int8_t* code_base = p.kv_codes + static_cast<int64_t>(b) * p.kv_stride[0] + static_cast<int64_t>(hkv_c) * p.kv_stride[1];
     const int64_t code_tok0 = (static_cast<int64_t>(b) * p.Hkv + hkv_c) * p.Skv;
-    // chunk `idx` (key idx / CPR of the tile, codes 16 (idx % CPR) ...) of tile jt: the codes and the key's scale / zp
+    // Chunk `idx` of a tile = 16 codes of one key.  Consecutive groups of four chunks walk down the keys inside one
+    // 64-column panel before moving to the next panel: the eight lanes of a quarter warp then store two rows of
+    // the same panel, whose 16-byte pieces land in eight different bank groups under the 128-byte swizzle (a whole
+    // 256-byte row per quarter warp would hit four bank groups twice).
+    auto chunk_row = [](int idx) { return (idx >> 2) % C::BN; };
+    auto chunk_col = [](int idx) { return (idx & 3) + 4 * (idx / (4 * C::BN)); };
+    // the codes of chunk `idx` of tile jt and the key's scale / zp
     auto load_chunk = [&](int jt, int idx, uint4& raw, uint32_t& szp) {
-      const int key = jt * C::BN + idx / CPR;
+      const int key = jt * C::BN + chunk_row(idx);
       raw = make_uint4(0, 0, 0, 0);
       szp = 0;
       if (key < p.Skv) {
-        raw = __ldg(reinterpret_cast<const uint4*>(code_base + static_cast<int64_t>(key) * p.kv_stride[2] + 16 * (idx % CPR)));
+        raw = __ldg(reinterpret_cast<const uint4*>(code_base + static_cast<int64_t>(key) * p.kv_stride[2] + 16 * chunk_col(idx)));
         szp = static_cast<uint32_t>(p.k_scale[code_tok0 + key]) |
               (static_cast<uint32_t>(static_cast<uint8_t>(p.k_zp[code_tok0 + key])) << 16);
       }
     };
     // ... dequantized and stored into V stage vs (keys past the end: zeros)
     auto store_chunk = [&](int vs, int idx, const uint4& raw, uint32_t szp) {
-      const int r = idx / CPR, c = idx % CPR;
+      const int r = chunk_row(idx), c = chunk_col(idx);
       const uint16_t sc = static_cast<uint16_t>(szp & 0xffffu);
       const int zp = static_cast<int8_t>(szp >> 16);
       uint4 lo, hi;
