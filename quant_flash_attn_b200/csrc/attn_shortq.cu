@@ -167,7 +167,17 @@ struct KvRing {
 #pragma unroll
     for (int i = 0; i < C::CHUNKS; ++i) {
       const int c = tid + i * C::THREADS;
-      const int r = c / C::CPR, cc = c % C::CPR;
+      int r = c / C::CPR, cc = c % C::CPR;
+      if constexpr (C::CPR == 8) {
+        // Head dim 128: a quarter warp (the unit a 16-byte shared-memory access is split into) takes chunks 0-3 of
+        // one row and chunks 4-7 of its neighbour instead of one whole row.  Its loads then cover two different
+        // 64-byte halves of the 128-byte code rows, and its stores land 272 + 128 bytes apart in the padded tile,
+        // i.e. in the other four 16-byte bank groups: both are conflict-free (a whole 256-byte row per quarter
+        // warp hits four bank groups twice on every store).
+        const int quad = c >> 2, k = quad & 3;
+        r = 2 * (quad >> 2) + (k & 1);
+        cc = 4 * (((k >> 1) ^ k) & 1) + (c & 3);
+      }
       uint4 v = make_uint4(0, 0, 0, 0);
       float2 m = make_float2(0.f, 0.f);
       if (tile * C::BN + r < skv) {          // rows past the end were not copied: keep them zero
