@@ -105,9 +105,9 @@ __device__ __forceinline__ void bwd_block(const uint32_t (&s)[8], const uint32_t
                                           uint32_t (&gw)[4]) {
   using H16 = Half16<T>;
   const float2 negM2 = make_float2(-12582912.0f, -12582912.0f);
-  const float4 z4 = meta[0], n4 = meta[1], s4 = meta[2];
+  const float4 z4 = lds128(meta), n4 = lds128(meta + 1), s4 = lds128(meta + 2);
   float4 l4 = make_float4(0.f, 0.f, 0.f, 0.f), d4 = l4;
-  if (KV_PASS) { l4 = meta[3]; d4 = meta[4]; }
+  if (KV_PASS) { l4 = lds128(meta + 3); d4 = lds128(meta + 4); }
 #pragma unroll
   for (int n = 0; n < 2; ++n) {
     const float2 z2 = n ? make_float2(z4.z, z4.w) : make_float2(z4.x, z4.y);
@@ -148,7 +148,7 @@ __device__ __forceinline__ void bwd_block_ref(const uint32_t (&s)[8], const uint
                                               uint32_t (&pw)[4], uint32_t (&gw)[4]) {
   using H16 = Half16<T>;
   float4 l4 = make_float4(0.f, 0.f, 0.f, 0.f), d4 = l4;
-  if (KV_PASS) { l4 = meta[3]; d4 = meta[4]; }
+  if (KV_PASS) { l4 = lds128(meta + 3); d4 = lds128(meta + 4); }
 #pragma unroll
   for (int n = 0; n < 2; ++n) {
     const float2 l2 = n ? make_float2(l4.z, l4.w) : make_float2(l4.x, l4.y);

@@ -191,7 +191,7 @@ __device__ __forceinline__ void softmax_block(const uint32_t (&s)[8], const floa
                                               uint32_t* pw) {
   using H16 = Half16<T>;
   const float2 negM2 = make_float2(-12582912.0f, -12582912.0f);
-  const float4 y4 = meta[0], z4 = meta[1], x4 = meta[2];
+  const float4 y4 = lds128(meta), z4 = lds128(meta + 1), x4 = lds128(meta + 2);
 #pragma unroll
   for (int n = 0; n < 2; ++n) {
     const float2 y2 = n ? make_float2(y4.z, y4.w) : make_float2(y4.x, y4.y);
@@ -710,10 +710,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           if (!ok) break;
 #pragma unroll
           for (int blk = 0; blk < C::BN / 16; ++blk) {
-            // an explicit shared-memory load: the generic load the compiler emits for this pointer measured 0.5 % slower
-            const uint32_t sa = smem_u32(meta + blk * 4);
-            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-                         : "=f"(xt[blk].x), "=f"(xt[blk].y), "=f"(xt[blk].z), "=f"(xt[blk].w) : "r"(sa));
+            xt[blk] = lds128(meta + blk * 4);
           }
         }
         if (ok) ok = mbar_wait(BAR(B_SFULL + t), j & 1, abort_flag, p.epoch);
